@@ -39,6 +39,9 @@ LIBRARIES = {
     "attention_split": ("attention_split.cu", []),
     "retention": ("retention.cu", []),
     "moe": ("moe.cu", []),
+    "stream": ("stream.cu", []),
+    "gla": ("gla.cu", []),
+    "attention_latent": ("attention_latent.cu", []),
     "gemm_tc": ("gemm_tcgen05.cu", []),
     "gemm_pair": ("gemm_tcgen05_pair.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),

@@ -4,18 +4,21 @@
 //                   has_gate, one more column: the logit of the shared expert's gate).  The `top` largest logits
 //                   choose the experts (of equal logits the lower index first); their weights are the softmax
 //                   over the chosen logits alone.  Written: idx [T, top] and wt [T, top] (either may be null), and
-//                   dense [T, E + has_gate]: an expert's weight where it was chosen, zero elsewhere, and
-//                   sigmoid(gate logit) in the last column.
+//                   dense [T, E + (has_gate != 0)]: an expert's weight where it was chosen, zero elsewhere, and
+//                   in the last column sigmoid(gate logit) (has_gate 1) or one (has_gate 2: a shared expert without
+//                   a gate; z then holds no column for it).  mode 1: the weight of a chosen expert is the sigmoid
+//                   of its own logit, not renormalised (the choice is by the same order).
 //   moe_dense_act   gu [T, 2 F] holds, for F = E ff + shared_ff columns, the gate rows and, F columns further, the
 //                   up rows of all experts (expert e owns columns e ff .. (e + 1) ff - 1, the shared expert the last
 //                   shared_ff).  a[t, c] = silu(gate) * up * dense[t, expert of c]: the experts a token did not
-//                   choose contribute zeros to the one product with all down matrices that follows.
+//                   choose contribute zeros to the one product with all down matrices that follows.  scale_input:
+//                   the weight multiplies the expert's input instead of its output, a = silu(w gate) * (w up).
 #include "common.cuh"
 
 namespace {
 
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, int* idx, float* wt, float* dense,
+moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, int mode, int* idx, float* wt, float* dense,
                  const int* __restrict__ tok_seq, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
@@ -54,7 +57,7 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
         if (bi == 0x7fffffff) break;         // fewer experts than `top`
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (j == 0) zmax = best;
-        const float p = expf(best - zmax);
+        const float p = mode == 1 ? 1.f / (1.f + expf(-best)) : expf(best - zmax);
         sum += p;
         if (lane == 0) {
             if (idx) idx[(size_t)t * top + j] = bi;
@@ -63,11 +66,11 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
         }
     }
     __syncwarp();
-    const float inv = 1.f / sum;
+    const float inv = mode == 1 ? 1.f : 1.f / sum;
     for (int i = 0, e = lane; e < E; e += 32, i++)
         if (taken >> i & 1u) drow[e] *= inv;
     if (wt) for (int j = lane; j < top; j += 32) wt[(size_t)t * top + j] *= inv;
-    if (has_gate && lane == 0) drow[E] = 1.f / (1.f + expf(-zr[E]));
+    if (has_gate && lane == 0) drow[E] = has_gate == 2 ? 1.f : 1.f / (1.f + expf(-zr[E]));
 }
 
 // One thread takes 8 consecutive columns of one token (16 bytes of bfloat16) where an expert's columns come in
@@ -75,7 +78,7 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
 // their gate and up values being read.
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
-moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W) {
+moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, int scale_input) {
     pdl_launch_dependents();
     pdl_wait();
     const int per_row = F / V;
@@ -98,8 +101,13 @@ moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F,
             }
 #pragma unroll
             for (int i = 0; i < V; i++) {
-                const float gf = to_f32(g[i]);
-                out[i] = from_f32<T>(gf / (1.f + expf(-gf)) * to_f32(u[i]) * w);
+                if (scale_input) {
+                    const float gf = to_f32(g[i]) * w;
+                    out[i] = from_f32<T>(gf / (1.f + expf(-gf)) * (to_f32(u[i]) * w));
+                } else {
+                    const float gf = to_f32(g[i]);
+                    out[i] = from_f32<T>(gf / (1.f + expf(-gf)) * to_f32(u[i]) * w);
+                }
             }
         } else {
 #pragma unroll
@@ -111,7 +119,8 @@ moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F,
 }
 
 template <typename T>
-int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, cudaStream_t st) {
+int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, int scale_input,
+               cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (F < 1 || ff < 1 || E < 0) return OE_ERR_UNSUPPORTED;
     // 16-byte pieces: bfloat16, every expert's columns and the row a multiple of 8, aligned pointers
@@ -120,28 +129,28 @@ int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vec)
-        return oe_launch(moe_dense_act_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W);
-    return oe_launch(moe_dense_act_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W);
+        return oe_launch(moe_dense_act_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input);
+    return oe_launch(moe_dense_act_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input);
 }
 
 }  // namespace
 
 extern "C" {
 
-int oe_moe_route(const float* z, long long ldz, int E, int top, int has_gate, int* idx, float* wt, float* dense,
+int oe_moe_route(const float* z, long long ldz, int E, int top, int has_gate, int mode, int* idx, float* wt, float* dense,
                  const int* tok_seq, int n_tokens, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (E < 1 || E > 1024 || top < 1) return OE_ERR_UNSUPPORTED;
-    return oe_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, st, z, ldz, E, top, has_gate, idx, wt, dense,
+    return oe_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, st, z, ldz, E, top, has_gate, mode, idx, wt, dense,
                      tok_seq, n_tokens);
 }
 int oe_moe_dense_act_f32(float* a, const float* gu, const float* dense, int n_tokens, int F, int E, int ff, int W,
-                         cudaStream_t st) {
-    return launch_act<float>(a, gu, dense, n_tokens, F, E, ff, W, st);
+                         int scale_input, cudaStream_t st) {
+    return launch_act<float>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, st);
 }
 int oe_moe_dense_act_bf16(bf16* a, const bf16* gu, const float* dense, int n_tokens, int F, int E, int ff, int W,
-                          cudaStream_t st) {
-    return launch_act<bf16>(a, gu, dense, n_tokens, F, E, ff, W, st);
+                          int scale_input, cudaStream_t st) {
+    return launch_act<bf16>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, st);
 }
 
 }  // extern "C"

@@ -63,8 +63,23 @@ _SIGNATURES = {
         "oe_retention_chunks": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P],
     },
     "moe": {
-        "oe_moe_route": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _P],
-        "oe_moe_dense_act": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "oe_moe_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P],
+        "oe_moe_dense_act": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "stream": {
+        "oe_group_rmsnorm": [_P, _P, _L, _P, _I, _I, _I, _F, _P],
+        "oe_group_rmsnorm_add": [_P, _P, _P, _I, _I, _I, _F, _F, _I, _P, _P],
+        "oe_poly_norm": [_P, _P, _L, _P, _I, _I, _F, _P],
+        "oe_side_gate": [_P, _P, _P, _L, _I, _I, _P, _P, _I, _I, _P],
+        "oe_depth_average": [_P, _P, _L, _P, _I, _L, _P],
+    },
+    "gla": {
+        "oe_gla_scan": [_P, _P, _P, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+    },
+    "attention_latent": {
+        "oe_latent_write": [_P, _L, _P, _F, _P, _L, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "oe_attn_latent": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+        "oe_head_matmul": [_P, _L, _L, _P, _L, _L, _P, _I, _I, _I, _I, _P],
     },
     "recurrent": {
         "oe_short_conv_prepare": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
@@ -82,7 +97,8 @@ _SIGNATURES = {
 }
 _TYPED = {"oe_embed_gather", "oe_rmsnorm", "oe_rope_kv_write", "oe_swiglu", "oe_gemm_simple", "oe_attn_paged",
           "oe_relu2", "oe_tanh_rows", "oe_rot_norm_kv_write", "oe_token_shift_mix", "oe_last_rows_to_state",
-          "oe_rope_split_kv_write", "oe_attn_split", "oe_moe_dense_act"}
+          "oe_rope_split_kv_write", "oe_attn_split", "oe_moe_dense_act", "oe_group_rmsnorm", "oe_poly_norm",
+          "oe_side_gate", "oe_latent_write", "oe_attn_latent", "oe_head_matmul"}
 _fn_cache: dict[str, object] = {}
 
 
@@ -483,17 +499,23 @@ def retention_scratch(n_tokens: int, n_seqs: int, heads: int, dk: int, dv: int) 
 
 # ---------------------------------------------------------------------------------------- moe.cu
 
-def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate: bool, dense: torch.Tensor, tok_seq: torch.Tensor,
-              idx: torch.Tensor | None = None, wt: torch.Tensor | None = None) -> None:
+def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate, dense: torch.Tensor, tok_seq: torch.Tensor,
+              idx: torch.Tensor | None = None, wt: torch.Tensor | None = None, weights: str = "softmax") -> None:
     """From router logits z float32 [T, >= E (+ 1)]: dense [T, E (+ 1)] float32 gets each chosen expert's weight
-    (softmax over the `top` largest logits alone; zero elsewhere) and, with has_gate, sigmoid of column E in its
-    last column; idx int32 [T, top] and wt float32 [T, top] receive the choice itself when given."""
+    (zero elsewhere) and, with has_gate, sigmoid of column E in its last column (has_gate "one": the constant 1, a
+    shared expert without a gate; z needs no column for it); idx int32 [T, top] and wt float32 [T, top] receive the
+    choice itself when given.  weights "softmax": the softmax over the `top` largest logits alone; "sigmoid": each
+    chosen expert's own sigmoid(logit), not renormalised."""
     _dev(z, dense, tok_seq, idx, wt)
     _i32(tok_seq, "tok_seq")
     _f32c(dense, "dense")
     T = z.shape[0]
     W = n_experts + int(bool(has_gate))
-    if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < W or tuple(dense.shape) != (T, W):
+    gate = 2 if has_gate == "one" else int(bool(has_gate))
+    if weights not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route: weights must be softmax or sigmoid, got {weights!r}")
+    if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < (n_experts if gate == 2 else W) \
+            or tuple(dense.shape) != (T, W):
         raise KernelError("moe_route: z float32 [T, >= E (+1)] and dense [T, E (+1)] expected")
     if top > n_experts:
         raise KernelError("moe_route: more experts chosen than there are")
@@ -504,13 +526,15 @@ def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate: bool, dense: 
     for t in (idx, wt):
         if t is not None and tuple(t.shape) != (T, top):
             raise KernelError("moe_route: idx and wt must be [T, top]")
-    _check(_fn("moe", "oe_moe_route")(_ptr(z), z.stride(0), n_experts, top, int(bool(has_gate)), _ptr(idx), _ptr(wt),
+    _check(_fn("moe", "oe_moe_route")(_ptr(z), z.stride(0), n_experts, top, gate, int(weights == "sigmoid"), _ptr(idx), _ptr(wt),
                                       _ptr(dense), _ptr(tok_seq), T, _stream()), "moe_route")
 
 
-def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int) -> None:
+def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int,
+                  scale_input: bool = False) -> None:
     """a[t, c] = silu(gu[t, c]) * gu[t, F + c] * dense[t, group of c]; the group of column c is c // ff for the
-    first n_experts * ff columns and the last column of dense for the rest (the shared expert)."""
+    first n_experts * ff columns and the last column of dense for the rest (the shared expert).  scale_input: the
+    weight w = dense[t, group] multiplies the expert's input instead, a = silu(w gu[t, c]) * (w gu[t, F + c])."""
     _dev(a, gu, dense)
     _f32c(dense, "dense")
     T, F = a.shape
@@ -519,7 +543,160 @@ def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_expe
             or (F > n_experts * ff and dense.shape[1] != n_experts + 1):
         raise KernelError("moe_dense_act: shapes do not agree")
     _check(_fn("moe", "oe_moe_dense_act", a.dtype)(_ptr(a), _ptr(gu), _ptr(dense), T, F, n_experts, ff, dense.shape[1],
-                                                   _stream()), "moe_dense_act")
+                                                   int(bool(scale_input)), _stream()), "moe_dense_act")
+
+
+# ---------------------------------------------------------------------------------------- stream.cu
+
+def group_rmsnorm(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, groups: int) -> None:
+    """y = x cut into `groups` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps), times w;
+    x float32 [rows, D], w float32 [D], y float32 or bfloat16."""
+    _dev(y, x, w)
+    _f32c(w, "w")
+    rows, D = x.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1 or y.shape != x.shape or not y.is_contiguous() or w.numel() != D \
+            or groups < 1 or D % groups:
+        raise KernelError("group_rmsnorm: x float32 (row stride free), y contiguous of x's shape, w [D], D a multiple of groups")
+    _check(_fn("stream", "oe_group_rmsnorm", y.dtype)(_ptr(y), _ptr(x), x.stride(0), _ptr(w), rows, D, int(groups), float(eps),
+                                                      _stream()), "group_rmsnorm")
+
+
+def group_rmsnorm_add(dst: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, groups: int, coef: float = 1.0,
+                      accumulate: bool = True, cast: torch.Tensor | None = None) -> None:
+    """dst (+)= coef * (the grouped norm of y) * w, all float32; cast (bfloat16, dst's shape) also receives the new dst."""
+    _dev(dst, y, w, cast)
+    for t, n in ((dst, "dst"), (y, "y"), (w, "w")):
+        _f32c(t, n)
+    rows, D = y.shape
+    if dst.shape != y.shape or w.numel() != D or groups < 1 or D % groups:
+        raise KernelError("group_rmsnorm_add: dst of y's shape, w [D], D a multiple of groups")
+    if cast is not None and (cast.dtype != torch.bfloat16 or cast.shape != dst.shape or not cast.is_contiguous()):
+        raise KernelError("group_rmsnorm_add: cast must be a contiguous bfloat16 tensor of dst's shape")
+    _check(_fn("stream", "oe_group_rmsnorm_add")(_ptr(dst), _ptr(y), _ptr(w), rows, D, int(groups), float(eps), float(coef),
+                                                 int(bool(accumulate)), _ptr(cast), _stream()), "group_rmsnorm_add")
+
+
+def poly_norm(out: torch.Tensor, z: torch.Tensor, coef: torch.Tensor, eps: float) -> None:
+    """out = a R(z) + b R(z^2) + c R(z^3) + e per row with R(u) = u / sqrt(mean(u^2) + eps) and (a, b, c, e) = coef
+    (float32 [4] on the device); z float32 [rows, F] (row stride free), out contiguous float32 or bfloat16."""
+    _dev(out, z, coef)
+    _f32c(coef, "coef")
+    rows, F = out.shape
+    if z.dtype != torch.float32 or z.shape != out.shape or z.stride(1) != 1 or not out.is_contiguous() or coef.numel() != 4:
+        raise KernelError("poly_norm: z float32 [rows, F], out contiguous of that shape, coef [4]")
+    _check(_fn("stream", "oe_poly_norm", out.dtype)(_ptr(out), _ptr(z), z.stride(0), _ptr(coef), rows, F, float(eps),
+                                                    _stream()), "poly_norm")
+
+
+def side_gate(g: torch.Tensor, u: torch.Tensor, table: torch.Tensor, offset: int, token_ids: torch.Tensor,
+              tok_seq: torch.Tensor) -> None:
+    """g[t, j] = gelu_tanh(u[t, j]) * table[token_ids[t], offset + j]; u float32 [T, dim] contiguous, g and table of
+    one dtype; rows of padding tokens and ids outside the table give zeros."""
+    _dev(g, u, table, token_ids, tok_seq)
+    _i32(token_ids, "token_ids")
+    _i32(tok_seq, "tok_seq")
+    _f32c(u, "u")
+    T, dim = u.shape
+    if g.shape != u.shape or not g.is_contiguous() or g.dtype != table.dtype or table.stride(1) != 1 \
+            or offset < 0 or offset + dim > table.shape[1] or token_ids.numel() < T or tok_seq.numel() < T:
+        raise KernelError("side_gate: g of u's shape and the table's dtype, offset + dim within the table's columns")
+    _check(_fn("stream", "oe_side_gate", g.dtype)(_ptr(g), _ptr(u), _ptr(table), table.stride(0), int(offset), dim,
+                                                  _ptr(token_ids), _ptr(tok_seq), table.shape[0], T, _stream()), "side_gate")
+
+
+def depth_average(x: torch.Tensor, hist: torch.Tensor, w: torch.Tensor, n: int) -> None:
+    """hist[n] = x; x = sum_{j <= n} w[j] * hist[j] (terms added in order of j); x float32 [T, D], hist float32
+    [>= n + 1, T, D], w float32 [>= n + 1]."""
+    _dev(x, hist, w)
+    for t, name in ((x, "x"), (hist, "hist"), (w, "w")):
+        _f32c(t, name)
+    if hist.dim() != 3 or tuple(hist.shape[1:]) != tuple(x.shape) or hist.shape[0] <= n or w.numel() <= n or n < 0:
+        raise KernelError("depth_average: hist [>= n + 1, T, D], w [>= n + 1]")
+    _check(_fn("stream", "oe_depth_average")(_ptr(x), _ptr(hist), hist.stride(0), _ptr(w), int(n), x.numel(), _stream()),
+           "depth_average")
+
+
+# ---------------------------------------------------------------------------------------- gla.cu
+
+def gla_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: int, off_k: int, off_v: int, z: torch.Tensor,
+             bias: torch.Tensor, ctx, heads: int, dk: int, dv: int, q_scale: float, tau: float) -> None:
+    """Per sequence and head, over the step's tokens in order: alpha = sigmoid(z + bias)^(1/tau) [dk];
+    S <- diag(alpha) S + k v^T; o = S^T (q * q_scale).  proj float32 rows holding q, k (heads*dk) and v (heads*dv) at
+    the given column offsets; z float32 [T, heads*dk]; state float32 [slots, heads, dk, dv]; o float32 [T, heads*dv]."""
+    _dev(o, state, proj, z, bias)
+    for t, n in ((o, "o"), (state, "state"), (bias, "bias")):
+        _f32c(t, n)
+    T = o.shape[0]
+    if proj.dtype != torch.float32 or z.dtype != torch.float32 or proj.stride(1) != 1 or z.stride(1) != 1 \
+            or proj.shape[0] < T or z.shape[0] < T or z.shape[1] < heads * dk or o.shape[1] != heads * dv \
+            or tuple(state.shape[1:]) != (heads, dk, dv) or bias.numel() != heads * dk \
+            or max(off_q, off_k) + heads * dk > proj.shape[1] or off_v + heads * dv > proj.shape[1]:
+        raise KernelError("gla_scan: shapes do not agree")
+    e = proj.element_size()
+    base = proj.data_ptr()
+    _check(_fn("gla", "oe_gla_scan")(_ptr(o), _ptr(state), base + off_q * e, base + off_k * e, base + off_v * e,
+                                     proj.stride(0), _ptr(z), z.stride(0), _ptr(bias), _ptr(ctx.seq_slot), _ptr(ctx.cu_q),
+                                     ctx.n_seqs, heads, dk, dv, float(q_scale), 1.0 / float(tau), _stream()), "gla_scan")
+
+
+# ---------------------------------------------------------------------------------------- attention_latent.cu
+
+def latent_write(d: torch.Tensor | None, w: torch.Tensor | None, eps: float, q: torch.Tensor, qfull: torch.Tensor,
+                 freq: torch.Tensor | None, dims: int, cache: torch.Tensor | None, tables: torch.Tensor, ctx, heads: int,
+                 dk: int, r: int, rd: int, write_cache: bool) -> None:
+    """Per token: the first r values of d's row, divided by their root mean square and times w, and the last rd
+    values with their first `dims` turned in pairs (2i, 2i + 1) by position * freq[i], go to the token's cache row
+    [r + rd] (only when write_cache); the last rd dimensions of each of q's heads [dk + rd] are turned the same way
+    and written to qfull[t, h, r:].  d float32; q, qfull and cache of one dtype."""
+    _dev(d, w, q, qfull, freq, cache, tables)
+    T = q.shape[0]
+    R = r + rd
+    if q.stride(1) != 1 or q.shape[1] < heads * (dk + rd) or tuple(qfull.shape) != (T, heads * R) \
+            or not qfull.is_contiguous() or q.dtype != qfull.dtype:
+        raise KernelError("latent_write: q [T, >= H (dk + rd)], qfull contiguous [T, H (r + rd)] of q's dtype")
+    if write_cache:
+        if d is None or w is None or cache is None or d.dtype != torch.float32 or d.stride(1) != 1 or d.shape[1] < R \
+                or w.dtype != torch.float32 or w.numel() != r or cache.dtype != q.dtype or not cache.is_contiguous() \
+                or tuple(cache.shape[1:]) != (PAGE, R):
+            raise KernelError("latent_write: d float32 [T, >= r + rd], w float32 [r], cache [pages, PAGE, r + rd]")
+    if dims and (freq is None or freq.dtype != torch.float32 or freq.numel() < dims // 2):
+        raise KernelError("latent_write: freq float32 [dims / 2]")
+    _check(_fn("attention_latent", "oe_latent_write", q.dtype)(
+        _ptr(d), 0 if d is None else d.stride(0), _ptr(w), float(eps), _ptr(q), q.stride(0), _ptr(qfull), _ptr(freq),
+        int(dims), _ptr(cache), _ptr(tables), tables.shape[1], _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), T, heads, dk, r, rd,
+        int(bool(write_cache)), _stream()), "latent_write")
+
+
+def attn_latent(out: torch.Tensor, qfull: torch.Tensor, cache: torch.Tensor, tables: torch.Tensor, ctx, heads: int, r: int,
+                rd: int, scale: float) -> None:
+    """out[t, h] = sum_j p_j c_j over the keys j <= pos of the token's sequence, p = softmax(scale * qfull[t, h] . row_j)
+    with row_j the cache row [r + rd] and c_j its first r values; float32 scores and sums."""
+    _dev(out, qfull, cache, tables)
+    T = qfull.shape[0]
+    R = r + rd
+    if tuple(qfull.shape) != (T, heads * R) or tuple(out.shape) != (T, heads * r) or out.dtype != qfull.dtype \
+            or cache.dtype != qfull.dtype or tuple(cache.shape[1:]) != (PAGE, R) \
+            or not (out.is_contiguous() and qfull.is_contiguous() and cache.is_contiguous()):
+        raise KernelError("attn_latent: shapes do not agree")
+    _check(_fn("attention_latent", "oe_attn_latent", out.dtype)(
+        _ptr(out), _ptr(qfull), _ptr(cache), _ptr(tables), tables.shape[1], _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), T, heads, r,
+        rd, float(scale), _stream()), "attn_latent")
+
+
+def head_matmul(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[t, h, :] = w[h] @ a[t, h, :] for all heads in one launch: a [T, H, K] and out [T, H, N] views whose last axis
+    is contiguous (token and head strides free), w [H, N, K] contiguous; a and w of one dtype, out of that dtype or float32."""
+    _dev(out, a, w)
+    T, H, K = a.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (H, N, K) or tuple(out.shape) != (T, H, N) or a.stride(2) != 1 or out.stride(2) != 1 \
+            or not w.is_contiguous() or a.dtype != w.dtype or out.dtype not in (a.dtype, torch.float32):
+        raise KernelError("head_matmul: a [T, H, K], w [H, N, K] of one dtype, out [T, H, N] of that dtype or float32")
+    fn = _fn("attention_latent", "oe_head_matmul", out.dtype) if out.dtype == a.dtype else \
+        _fn("attention_latent", "oe_head_matmul", out.dtype, in_dtype=a.dtype)
+    _check(fn(
+        _ptr(out), out.stride(0), out.stride(1), _ptr(a), a.stride(0), a.stride(1), _ptr(w), T, H, N, K, _stream()),
+        "head_matmul")
 
 
 # ---------------------------------------------------------------------------------------- recurrent.cu

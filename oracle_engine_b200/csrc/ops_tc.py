@@ -621,3 +621,10 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
     ops._check(code, "attention_split_mma")
     if n_splits > 1:
         ops.LAUNCHES[0] += 1
+
+
+# ---------------------------------------------------------------------------------------- a cache of latents
+
+def attention_latent_supported(n_heads: int, r: int, rd: int) -> bool:
+    """Whether a tensor-core kernel takes the attention over latent rows [r + rd] (parts/latent_attention.py)."""
+    return False

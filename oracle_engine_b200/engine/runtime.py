@@ -39,6 +39,9 @@ class Runtime:
     # add_into(..., keep_cast=True)): (address of the stream, the copy).  `activations` takes it instead of casting
     # again; the model clears it when a forward pass starts.
     cast_cache: tuple | None = None
+    # Tensors that parts of different layers share during ONE forward pass (a history of the stream, say): the part
+    # that runs first puts them here, the others find them.  While a CUDA graph is captured they are the graph's memory.
+    pass_store: dict = field(default_factory=dict, repr=False)
     _buffers: dict = field(default_factory=dict, repr=False)
     _cast_turn: int = 0
 

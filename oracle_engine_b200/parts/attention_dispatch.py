@@ -59,3 +59,14 @@ def split_mixer_core(rt, out, qkv, cos, sin, rot, kcache, vcache, tables, ctx, H
             ops_tc.attention_split(out, qkv, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap)
             return
     ops.attn_split(out, qkv, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap)
+
+
+def latent_core(rt, out, qfull, rows, tables, ctx, H, r, rd, scale) -> None:
+    """Attention of absorbed queries [T, H (r + rd)] over a cache of latent rows [r + rd]; out [T, H r] gets each
+    head's weighted sum of the latents (parts/latent_attention.py)."""
+    if rt.dtype == torch.bfloat16 and rt.tensor_cores:
+        from ..csrc import ops_tc
+        if ops_tc.attention_latent_supported(H, r, rd):
+            ops_tc.attention_latent(out, qfull, rows, tables, ctx, H, r, rd, scale)
+            return
+    ops.attn_latent(out, qfull, rows, tables, ctx, H, r, rd, scale)

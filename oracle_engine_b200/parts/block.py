@@ -4,7 +4,9 @@ outputs into the float32 residual stream themselves (fused into their last produ
 `norm_after`: x += norm(mixer(x)); x += norm(ffn(x)): the sublayers read the residual stream itself and
 their OUTPUT is normed before it is added; a sublayer adds its output into a zeroed float32 buffer.
 `pre_norm_scaled`: x += m * s1 * mixer(norm(x)); x += m * s2 * ffn(norm(x)) with m one constant and s1, s2 one
-weight per channel each (a layer scale)."""
+weight per channel each (a layer scale).
+`sandwich`: x += norm_1b(mixer(norm_1(x))); x += norm_2b(ffn(norm_2(x))): a norm before and after every sublayer;
+optionally followed by a per-token side input (`TokenSide`) and an average over the depth (`DepthAverage`)."""
 from __future__ import annotations
 
 import torch
@@ -147,6 +149,138 @@ class PreNormScaledBlock:
         self._sublayer(self.mixer, "mixer", self.mixer_norm.forward(x), x, ctx, cache, state, owns_cache)
         if self.feed_forward is not None:
             self._sublayer(self.feed_forward, "ffn", self.ffn_norm.forward(x), x, ctx)
+
+
+class TokenSide(Part):
+    """A per-token input added to the stream: every layer owns `dim` columns of a second embedding table,
+        e = table[token][off : off + dim];  g = gelu_tanh(Wg x) * e;  y = Wp g;  x <- x + y / sqrt(mean(y^2) + eps) * w
+    params: hidden_size, vocab_size, dim, offset (the layer's first column of the table), table_width, eps,
+    names {table, gate, proj, norm} (the table's name is not under the layer's prefix)."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.D, self.V = int(self._need("hidden_size")), int(self._need("vocab_size"))
+        self.dim, self.offset = int(self._need("dim")), int(self._need("offset"))
+        self.table_width = int(self._need("table_width"))
+        self.eps = float(self._need("eps"))
+        n = self._need("names")
+        self.names = {"table": n["table"], "gate": prefix + n["gate"], "proj": prefix + n["proj"], "norm": prefix + n["norm"]}
+        self.table = self.w_gate = self.w_proj = self.norm_w = None
+
+    def tensors(self):
+        n = self.names
+        return [TensorDecl(n["table"], (self.V, self.table_width)), TensorDecl(n["gate"], (self.dim, self.D)),
+                TensorDecl(n["proj"], (self.D, self.dim)), TensorDecl(n["norm"], (self.D,), "ones_normal")]
+
+    def load(self, get):
+        n = self.names
+        # the layer keeps its own columns of the table only
+        self.table = self.rt.to_compute(get(n["table"])[:, self.offset:self.offset + self.dim])
+        self.w_gate, self.w_proj = self.rt.to_compute(get(n["gate"])), self.rt.to_compute(get(n["proj"]))
+        self.norm_w = self.rt.to_f32(get(n["norm"]))
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gate, self.w_proj) if t is not None)
+
+    def flops(self, start, count):
+        return count * 4.0 * self.D * self.dim
+
+    def forward(self, x, ctx):
+        from .linear import matmul_nt
+        T = x.shape[0]
+        u = self.rt.buffer("side.u", T, self.dim, dtype=torch.float32)
+        matmul_nt(self.rt, u, self.rt.activations(x), self.w_gate)
+        g = self.rt.buffer("side.g", T, self.dim)
+        ops.side_gate(g, u, self.table, 0, ctx.token_ids, ctx.tok_seq)
+        y = self.rt.buffer("side.y", T, self.D, dtype=torch.float32)
+        matmul_nt(self.rt, y, g, self.w_proj)
+        ops.rmsnorm_add(x, y, self.norm_w, self.eps)
+
+
+class DepthAverage(Part):
+    """What leaves layer n (n = 0 for the first) is a weighted sum over the depth: with X_0 the stream that entered
+    the first layer and X_(j+1) the result of layer j, x <- sum_{j <= n + 1} a[j] X_j, a the layer's own n + 2 weights.
+    The X_j of a forward pass are kept in one float32 buffer [layers + 1, tokens, hidden] that lives for the pass.
+    params: hidden_size, index (n), layers, name."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.D = int(self._need("hidden_size"))
+        self.index, self.layers = int(self._need("index")), int(self._need("layers"))
+        self.name = prefix + self._need("name")
+        self.weights = None
+
+    def tensors(self):
+        return [TensorDecl(self.name, (self.index + 2,), "ones_normal")]
+
+    def load(self, get):
+        self.weights = self.rt.to_f32(get(self.name))
+
+    def enter(self, x):
+        """The first layer makes the pass's buffer and keeps the entering stream in it; the others find it."""
+        if self.index == 0:
+            hist = self.rt.buffer("depth.history", self.layers + 1, x.shape[0], x.shape[1], dtype=torch.float32)
+            self.rt.pass_store["depth.history"] = hist
+            hist[0].copy_(x)
+
+    def leave(self, x):
+        hist = self.rt.pass_store.get("depth.history")
+        if hist is None or tuple(hist.shape[1:]) != tuple(x.shape):
+            raise ValueError("depth_average: the first layer of the pass has not run")
+        ops.depth_average(x, hist, self.weights, self.index + 1)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock:
+    """x <- x + norm_1b(mixer(norm_1(x))); x <- x + norm_2b(ffn(norm_2(x))) (the second only with a feed-forward); then
+    the token side input and the depth average, where the layer has them.
+    params: hidden_size, mixer_out_norm / ffn_out_norm (PartSpec-like {kind, params} of the norms applied to the
+    sublayers' outputs), token_side (params of `TokenSide`, or None), depth_average (params of `DepthAverage`, or None)."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, params, prefix, runtime):
+        from .registry import NORMS
+        if mixer_norm is None or (feed_forward is not None and ffn_norm is None):
+            raise ValueError("sandwich: every sublayer needs the norm of its input")
+        self.mixer, self.feed_forward, self.mixer_norm, self.ffn_norm = mixer, feed_forward, mixer_norm, ffn_norm
+        self.rt = runtime
+
+        def out_norm(key):
+            spec = params[key]
+            return NORMS.get(spec["kind"])(spec["params"], prefix, runtime)
+        self.mixer_out_norm = out_norm("mixer_out_norm")
+        self.ffn_out_norm = out_norm("ffn_out_norm") if feed_forward is not None else None
+        self.side = TokenSide(params["token_side"], prefix, runtime) if params.get("token_side") else None
+        self.depth = DepthAverage(params["depth_average"], prefix, runtime) if params.get("depth_average") else None
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.ffn_norm, self.feed_forward,
+                            self.ffn_out_norm, self.side, self.depth) if p is not None]
+
+    def first_weights(self):
+        return _first_weights(self.mixer)
+
+    def _sublayer(self, part, out_norm, h, x, *args):
+        y = self.rt.buffer("sublayer_out", *x.shape, dtype=torch.float32)
+        if getattr(part, "can_overwrite", False):
+            part.forward(h, y, *args, overwrite=True)
+        else:
+            y.zero_()
+            part.forward(h, y, *args)
+        out_norm.add_into(x, y)
+
+    def forward(self, x, ctx, cache, state, owns_cache=True):
+        self.rt.next_weights = None
+        if self.depth is not None:
+            self.depth.enter(x)
+        self._sublayer(self.mixer, self.mixer_out_norm, self.mixer_norm.forward(x), x, ctx, cache, state, owns_cache)
+        if self.feed_forward is not None:
+            self._sublayer(self.feed_forward, self.ffn_out_norm, self.ffn_norm.forward(x), x, ctx)
+        if self.side is not None:
+            self.side.forward(x, ctx)
+        if self.depth is not None:
+            self.depth.leave(x)
 
 
 def _first_weights(part):

@@ -102,3 +102,49 @@ class SquaredReLU(Part):
         matmul_nt(self.rt, a, h, self.w_up)
         ops.relu2_(a)
         matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)
+
+
+@FEED_FORWARDS.register("poly_norm_mlp")
+class PolyNormMLP(Part):
+    """x += Wd P(Wu h) with P(z) = a R(z) + b R(z^2) + c R(z^3) + e: powers element by element, R(u) = u / sqrt(mean(u^2)
+    + eps) over a token's intermediate values, (a, b, c, e) a weight tensor of four numbers.  The up product leaves
+    float32 (the norms' sums are float32 sums of float32 values); P writes the compute dtype.
+    params: hidden_size, intermediate_size, eps, tensor_names (optional overrides of "up", "down", "act")."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.D = int(self._need("hidden_size"))
+        self.FF = int(self._need("intermediate_size"))
+        self.eps = float(self._need("eps"))
+        names = {"up": "mlp.up", "down": "mlp.down", "act": "mlp.act", **self.params.get("tensor_names", {})}
+        self.names = {k: prefix + v for k, v in names.items()}
+        self.w_up = self.w_down = self.coef = None
+
+    def tensors(self):
+        return [TensorDecl(self.names["up"], (self.FF, self.D)), TensorDecl(self.names["down"], (self.D, self.FF)),
+                TensorDecl(self.names["act"], (4,), "ones_normal")]
+
+    def load(self, get):
+        self.w_up = self.rt.to_compute(get(self.names["up"]))
+        self.w_down = self.rt.to_compute(get(self.names["down"]))
+        self.coef = self.rt.to_f32(get(self.names["act"]))
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down) if t is not None)
+
+    def flops(self, start, count):
+        return count * 2.0 * 2 * self.D * self.FF
+
+    def first_weights(self):
+        return self.w_up
+
+    def forward(self, h, residual, ctx, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
+        T = h.shape[0]
+        z = self.rt.buffer("polynorm.z", T, self.FF, dtype=torch.float32)
+        matmul_nt(self.rt, z, h, self.w_up)
+        a = self.rt.buffer("polynorm.a", T, self.FF)
+        ops.poly_norm(a, z, self.coef, self.eps)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)

@@ -16,6 +16,7 @@ from .spec import ModelSpec, TensorDecl
 from . import attention, block, embedding, feedforward, norms, positions  # noqa: F401,E402
 from . import delta_rule, parallel, sink_attention, time_mix  # noqa: F401,E402
 from . import capped_attention, moe, retention  # noqa: F401,E402
+from . import gla, latent_attention  # noqa: F401,E402
 
 
 class DecoderModel:

@@ -3,6 +3,9 @@
     z = Wr h (float32);  the `top` experts with the largest z are chosen, their weights w_e are the softmax over the
     chosen z alone;  E_e(h) = Wdown_e (silu(Wgate_e h) * (Wup_e h));
     y = sum_chosen w_e E_e(h) + sigmoid(Wsg h) * E_shared(h)                   (the second term only with a shared expert)
+Variants by parameter: the weights may be each chosen expert's own sigmoid(z_e), not renormalised; the weight may
+multiply the expert's input, y = sum_chosen E_e(w_e h) (its gate and up rows are linear in the input, so the kernel
+scales those: silu(w_e g) * (w_e u)); the shared expert may be added without a gate.
 
 How it is computed: the experts stand side by side.  One product with all gate and up matrices (the shared expert's
 behind the routed ones), one kernel that applies silu(gate) * up and multiplies each expert's columns by the token's
@@ -27,7 +30,10 @@ from .spec import TensorDecl
 class MoESwiGLU(Part):
     graph_safe = True
     can_overwrite = True
-    """params: hidden_size, num_experts, top, expert_size, shared_size (0 or None: no shared expert), tensor_names
+    """params: hidden_size, num_experts, top, expert_size, shared_size (0 or None: no shared expert), router_weights
+    ("softmax", the default: the softmax over the chosen logits alone; "sigmoid": each chosen expert's own
+    sigmoid(logit), not renormalised), weight_on ("output", the default: y = sum w_e E_e(h); "input": y = sum E_e(w_e h)),
+    shared_gate (default True: the shared expert's output times sigmoid(Wsg h); False: added as it is), tensor_names
     (optional overrides of "expert" (a format with {e}), "router", "shared", "shared_gate")."""
 
     def __init__(self, params, prefix, runtime):
@@ -37,6 +43,11 @@ class MoESwiGLU(Part):
         self.top = int(self._need("top"))
         self.ff = int(self._need("expert_size"))
         self.sff = int(self.params.get("shared_size") or 0)
+        self.router_weights = self.params.get("router_weights") or "softmax"
+        self.weight_on = self.params.get("weight_on") or "output"
+        self.shared_gate = bool(self.params.get("shared_gate", True)) and self.sff > 0
+        if self.router_weights not in ("softmax", "sigmoid") or self.weight_on not in ("output", "input"):
+            raise ValueError("moe_swiglu: router_weights is softmax or sigmoid, weight_on is output or input")
         if not 1 <= self.top <= self.E:
             raise ValueError(f"moe_swiglu: top {self.top} of {self.E} experts")
         if self.E > 1024:
@@ -58,7 +69,7 @@ class MoESwiGLU(Part):
             out += [TensorDecl(p + "gate", (f, self.D)), TensorDecl(p + "up", (f, self.D)),
                     TensorDecl(p + "down", (self.D, f))]
         out.append(TensorDecl(self.names["router"], (self.E, self.D)))
-        if self.sff:
+        if self.shared_gate:
             out.append(TensorDecl(self.names["shared_gate"], (1, self.D)))
         return out
 
@@ -67,7 +78,7 @@ class MoESwiGLU(Part):
         ex = self._expert_names()
         self.w_gu = torch.cat([to(get(p + "gate")) for p in ex] + [to(get(p + "up")) for p in ex], 0).contiguous()
         self.w_down = torch.cat([to(get(p + "down")) for p in ex], 1).contiguous()
-        route = [to(get(self.names["router"]))] + ([to(get(self.names["shared_gate"]))] if self.sff else [])
+        route = [to(get(self.names["router"]))] + ([to(get(self.names["shared_gate"]))] if self.shared_gate else [])
         self.w_route = torch.cat(route, 0).contiguous()
 
     def weight_bytes(self):
@@ -77,20 +88,21 @@ class MoESwiGLU(Part):
         return count * 2.0 * self.D * (3 * self.F + self.w_route_rows())
 
     def w_route_rows(self):
-        return self.E + (1 if self.sff else 0)
+        return self.E + (1 if self.shared_gate else 0)
 
     def first_weights(self):
         return self.w_gu
 
     def forward(self, h, residual, ctx, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
-        T, W = h.shape[0], self.w_route_rows()
-        z = self.rt.buffer("moe.z", T, W, dtype=torch.float32)
+        T = h.shape[0]
+        z = self.rt.buffer("moe.z", T, self.w_route_rows(), dtype=torch.float32)
         matmul_nt(self.rt, z, h, self.w_route)                  # float32 sums and output on both paths
-        dense = self.rt.buffer("moe.dense", T, W, dtype=torch.float32)
-        ops.moe_route(z, self.E, self.top, bool(self.sff), dense, ctx.tok_seq)
+        dense = self.rt.buffer("moe.dense", T, self.E + (1 if self.sff else 0), dtype=torch.float32)
+        ops.moe_route(z, self.E, self.top, (True if self.shared_gate else "one") if self.sff else False, dense,
+                      ctx.tok_seq, weights=self.router_weights)
         gu = self.rt.buffer("moe.gu", T, 2 * self.F)
         matmul_nt(self.rt, gu, h, self.w_gu)
         a = self.rt.buffer("moe.a", T, self.F)
-        ops.moe_dense_act(a, gu, dense, self.E, self.ff)
+        ops.moe_dense_act(a, gu, dense, self.E, self.ff, scale_input=self.weight_on == "input")
         matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)

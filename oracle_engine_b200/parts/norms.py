@@ -2,7 +2,8 @@
 computed in float32 and stored in the compute dtype (reference: core/ops.cpp:149-195; the
 epsilon is a parameter here, always passed).  `add_into(dst, y, coef)` is the same norm applied to a
 sublayer's float32 OUTPUT and added, times coef, into another float32 tensor (layers that norm what
-a sublayer returns instead of what it reads)."""
+a sublayer returns instead of what it reads).  With `groups` > 1 the row is cut into that many equal consecutive parts
+and each part is divided by its own root mean square (the weight still spans the whole row)."""
 from __future__ import annotations
 
 from ..csrc import ops
@@ -14,7 +15,7 @@ from .spec import TensorDecl
 class RMSNorm(Part):
     graph_safe = True
     """params: size, eps, name (tensor name under the prefix), offset (added to the stored weight: 1.0 for a
-    weight that is kept around zero, y = x / rms * (1 + w); default 0)."""
+    weight that is kept around zero, y = x / rms * (1 + w); default 0), groups (default 1)."""
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
@@ -22,6 +23,9 @@ class RMSNorm(Part):
         self.eps = float(self._need("eps"))
         self.name = prefix + self._need("name")
         self.offset = float(self.params.get("offset", 0.0) or 0.0)
+        self.groups = int(self.params.get("groups") or 1)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"rms_norm: {self.size} values do not split into {self.groups} equal groups")
         self.weight = None
 
     def tensors(self):
@@ -37,7 +41,10 @@ class RMSNorm(Part):
 
     def forward(self, x):
         y = self.rt.empty(*x.shape)
-        ops.rmsnorm(y, x, self.weight, self.eps)
+        if self.groups > 1:
+            ops.group_rmsnorm(y, x, self.weight, self.eps, self.groups)
+        else:
+            ops.rmsnorm(y, x, self.weight, self.eps)
         return y
 
     def add_into(self, dst, y, coef: float = 1.0, accumulate: bool = True, keep_cast: bool = False) -> None:
@@ -49,4 +56,7 @@ class RMSNorm(Part):
             self.rt._cast_turn ^= 1
             cast = self.rt.buffer(f"stream_copy{self.rt._cast_turn}", *dst.shape)
             self.rt.cast_cache = (dst.data_ptr(), cast)
-        ops.rmsnorm_add(dst, y, self.weight, self.eps, coef, accumulate, cast)
+        if self.groups > 1:
+            ops.group_rmsnorm_add(dst, y, self.weight, self.eps, self.groups, coef, accumulate, cast)
+        else:
+            ops.rmsnorm_add(dst, y, self.weight, self.eps, coef, accumulate, cast)
