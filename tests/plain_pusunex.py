@@ -216,3 +216,31 @@ def forward(cfg, w, tokens, return_layers=False):
 def load(folder):
     folder = Path(folder)
     return json.loads((folder / "config.json").read_text()), read_safetensors(folder / "model.safetensors")
+
+
+class PlainPusunex:
+    """A model folder read by this file alone."""
+
+    def __init__(self, folder):
+        self.cfg, self.w = load(folder)
+
+    def logits(self, tokens):
+        return forward(self.cfg, self.w, tokens)
+
+    def layers(self, tokens):
+        """The stream that leaves every layer (after the depth average), [layers, T, D]."""
+        _, pre = forward(self.cfg, self.w, tokens, return_layers=True)
+        hist, out = [self.w["embed"][torch.as_tensor(tokens, dtype=torch.long)]], []
+        for i in range(len(pre)):
+            hist.append(pre[i])
+            a = self.w[f"l{i}.dwa"]
+            out.append(sum(a[j] * hist[j] for j in range(i + 2)))
+        return torch.stack(out)
+
+
+def generate(plain, prompt, n_new):
+    """Greedy continuation, the whole sequence recomputed for every token."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain.logits(toks)[-1].argmax()))
+    return toks[len(prompt):]

@@ -1,0 +1,293 @@
+"""The Pusunex design on the GPU against the plain float64 model of tests/plain_pusunex.py: every layer by itself,
+whole prompts, token-by-token decoding, prompts in pieces down to two tokens, ragged batches, reused slots, keys far
+away and at page borders under a peaked softmax, a recurrent state that remembers the first token for hundreds of
+steps, sizes of real models, and greedy generation through Engine.generate and the command line."""
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_pusunex as pp
+import pusunex_models as pm
+
+pytestmark = pytest.mark.gpu
+
+# A position's error is the root mean square over the vocabulary of the difference of its logits, relative to
+# the root mean square of the request's logits.  float32: rounding of a few hundred fused multiply-adds per
+# value; bfloat16: activations rounded to 2^-9 relative at every product, a few dozen products deep.
+TOL = {"float32": 1e-4, "bfloat16": 5e-2}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, (raw, seed) in pm.ALL.items():
+        d = pm.write(tmp_path_factory.mktemp(f"pusunex_{name}"), raw, seed,
+                     decay_bias=7.0 if name == "LONG_MEMORY" else 3.0)
+        out[name] = (d, pp.PlainPusunex(d))
+    return out
+
+
+def _engine(folder, dtype, **kw):
+    from oracle_engine_b200.engine.engine import Engine
+    kw.setdefault("max_tokens", 1024)
+    return Engine.from_pretrained(folder, dtype=dtype, **kw)
+
+
+def _compare(got, plain, requests, tol, what, cache={}):
+    for i, toks in enumerate(requests):
+        key = (id(plain), tuple(toks))
+        if key not in cache:
+            cache[key] = plain.logits(toks).numpy()
+        want = cache[key]
+        assert not np.isnan(got[i]).any(), f"{what}: request {i} has positions without logits"
+        err = np.sqrt(((got[i] - want) ** 2).mean(axis=1)) / np.sqrt((want ** 2).mean())
+        assert err.max() < tol, f"{what}: request {i} (len {len(toks)}) first bad position " \
+                                f"{int((err >= tol).argmax())}, worst {int(err.argmax())}: {err.max()}"
+
+
+def _run(eng, tmp, steps, requests):
+    got = helpers.collect(steps, helpers.TraceRunner(eng, tmp).run(steps), requests)
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.n_slots
+    return got
+
+
+@pytest.mark.parametrize("name", ["P1", "P2", "P3"])
+def test_every_layer_by_itself_float32(models, name):
+    """The stream that leaves each layer of a whole prompt, in float32, against the plain model; then the same
+    prompt's last 20 tokens one by one."""
+    from oracle_engine_b200 import SequenceStep
+    folder, plain = models[name]
+    eng = _engine(folder, "float32", use_graphs=False)
+    seen = []
+    for layer in eng.model.layers:
+        def fwd(x, *a, _orig=layer.forward, **k):
+            _orig(x, *a, **k)
+            seen.append(x.detach().double().cpu())
+        layer.forward = fwd
+    toks = helpers.random_tokens(150, plain.cfg["vocab"], 9)
+    want = plain.layers(toks)
+    slot = eng.alloc()
+    eng.step([SequenceStep(slot, toks[:130], [129])])
+    assert len(seen) == len(want) == len(plain.cfg["layers"])
+    for i, (a, b) in enumerate(zip(seen, want)):
+        err = (a - b[:130]).abs().max().item()
+        assert err < 2e-4 * max(1.0, b.abs().max().item()), \
+            f"{name}: layer {i} ({plain.cfg['layers'][i]['type']}, {(plain.cfg['layers'][i]['mlp'] or {}).get('kind')}) differs by {err}"
+    for t in range(130, 150):
+        seen.clear()
+        eng.step([SequenceStep(slot, toks[t:t + 1], [0])])
+        for i, (a, b) in enumerate(zip(seen, want)):
+            err = (a[0] - b[t]).abs().max().item()
+            assert err < 2e-4 * max(1.0, b.abs().max().item()), f"{name}: token {t} alone, layer {i} differs by {err}"
+    eng.free(slot)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P1", "P2", "P3"])
+def test_whole_decoded_pieces_and_batches_agree_with_plain(models, tmp_path, name, dtype):
+    folder, plain = models[name]
+    vocab = plain.cfg["vocab"]
+    lens = [130, 65, 1, 200, 37, 2, 64, 129]
+    requests = [helpers.random_tokens(n, vocab, 300 + i) for i, n in enumerate(lens)]
+    eng = _engine(folder, dtype)
+    runs = {}
+    # each alone and whole; each alone decoded token by token from the first token (or after a prompt)
+    runs["whole"] = helpers.whole_steps(requests)
+    runs["decoded"] = helpers.tail_steps(requests, 1000)
+    runs["tail"] = helpers.tail_steps(requests, 40)
+    # in pieces down to two tokens and one
+    runs["pieces"] = helpers.piece_steps(requests, [helpers.cut(n, [2, 37, 1, 64, 3, 65]) for n in lens], batch_size=1)
+    runs["pairs"] = helpers.piece_steps(requests[1:3] + requests[4:6], [helpers.cut(n, [2]) for n in (65, 1, 37, 2)],
+                                        batch_size=1)
+    # ragged batches of three, prompts then one token each; the next batch takes the slots they leave
+    runs["batched"] = helpers.batched_steps(requests, [max(1, n - 20) for n in lens], 3)
+    # steps that mix a prompt piece of one request with single tokens of others
+    runs["mixed"] = helpers.piece_steps(requests, [helpers.cut(n, [1, 1, 30, 1, 2, 70][i % 3:] + [5]) for i, n in enumerate(lens)],
+                                        batch_size=3)
+    got = {}
+    for k, steps in runs.items():
+        reqs = requests[1:3] + requests[4:6] if k == "pairs" else requests
+        got[k] = _run(eng, tmp_path / k, steps, reqs)
+        _compare(got[k], plain, reqs, TOL[dtype], f"{name} {dtype} {k}")
+    if dtype == "float32":
+        # a position's logits do not depend on the cut or the batch: the same instructions in the same order
+        for k in got:
+            reqs = [1, 2, 4, 5] if k == "pairs" else range(len(requests))
+            for j, i in enumerate(reqs):
+                assert np.array_equal(got["whole"][i], got[k][j]), f"{name} float32: {k} differs from whole, request {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_and_page_borders_under_a_peaked_softmax(models, tmp_path, dtype):
+    """Prompts that end just before, at and just after a page border, decoded across the next one, with attentions
+    in which single keys (far ones too) decide: a lost or misplaced latent changes the logits."""
+    folder, plain = models["SHARP"]
+    vocab = plain.cfg["vocab"]
+    toks = helpers.random_tokens(300, vocab, 77)
+    # the softmax is peaked, and for the last token the key that decides lies far back
+    w, m, eps = plain.w, plain.cfg["layers"][0]["mixer"], plain.cfg["norm"]["eps"]
+    h = pp.group_norm(w["embed"][torch.as_tensor(toks)], w["l0.norm1"], eps, plain.cfg["norm"]["groups"])
+    c, _ = pp.latent_of(h, w, "l0.mix.", m, eps, torch.arange(300))
+    q = (h @ w["l0.mix.q"].T).reshape(300, m["heads"], m["dim"])
+    k = (c @ w["l0.mix.uk"].T).reshape(300, m["heads"], m["dim"])
+    peaks, far = [], 0
+    for t in (128, 200, 299):
+        for hh in range(m["heads"]):
+            p = torch.softmax((k[:t + 1, hh] @ q[t, hh]) * m["scale"], 0)
+            peaks.append(float(p.max()))
+            far += int(p.argmax()) < t - 64
+    assert np.median(peaks) > 0.2 and far >= 6
+    lens = [63, 64, 65, 127, 128, 129, 300]
+    requests = [toks[:n] for n in lens]
+    eng = _engine(folder, dtype)
+    runs = {"whole": helpers.whole_steps(requests),
+            "tail": helpers.tail_steps(requests, 6),
+            "pieces": helpers.piece_steps(requests, [helpers.cut(n, [62, 2, 1, 63, 64]) for n in lens], batch_size=2)}
+    for kname, steps in runs.items():
+        got = _run(eng, tmp_path / kname, steps, requests)
+        _compare(got, plain, requests, TOL[dtype] * 2, f"SHARP {dtype} {kname}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_state_that_remembers_the_first_token(models, tmp_path, dtype):
+    """Linear attention only (no paged cache at all), decays so close to one that the first token still weighs after
+    hundreds: a state that is dropped, zeroed at a step's start or taken from another slot changes the logits."""
+    folder, plain = models["LONG_MEMORY"]
+    vocab = plain.cfg["vocab"]
+    toks = helpers.random_tokens(400, vocab, 5)
+    # in float32 one other first token shows 399 tokens later; in bfloat16 other first 30 tokens do
+    n_other = 1 if dtype == "float32" else 30
+    other = [(t + 1) % vocab for t in toks[:n_other]] + toks[n_other:]
+    a, b = plain.logits(toks)[-1], plain.logits(other)[-1]
+    apart = float((a - b).pow(2).mean().sqrt())
+    assert apart / float(a.pow(2).mean().sqrt()) > (4e-3 if dtype == "float32" else 4e-2)
+    requests = [toks, other, toks[:70], toks[:3]]
+    eng = _engine(folder, dtype, max_tokens=2048)
+    assert len(eng.cache.groups) == 0
+    runs = {"tail": helpers.tail_steps(requests, 330),
+            "batched": helpers.batched_steps(requests, [60, 1, 66, 2], 4),
+            "pieces": helpers.piece_steps(requests, [helpers.cut(len(r), [2, 100, 1, 7]) for r in requests], batch_size=2)}
+    for k, steps in runs.items():
+        got = _run(eng, tmp_path / k, steps, requests)
+        _compare(got, plain, requests, TOL[dtype], f"LONG_MEMORY {dtype} {k}")
+        for mine, want in ((got[0][-1], a), (got[1][-1], b)):
+            off = float(np.sqrt(((mine - want.numpy()) ** 2).mean()))
+            assert off < apart / 3, f"LONG_MEMORY {dtype} {k}: the last token is {off} off, the two requests {apart} apart"
+
+
+def test_a_layer_that_reads_another_layers_latents(tmp_path):
+    """The reading layer sees the owner's rows, not a cache of its own and not rows of a third layer: with the
+    owner's down projection changed, the reader's part of the output changes as the plain model's does."""
+    from oracle_engine_b200.weights.safetensors_io import ModelFiles, write_safetensors
+    raw = pm.config(120, 64, 1e-5, 2, 0, [
+        pm.layer(pm.latent(2, 16, 16, 24, 0.3)),
+        pm.layer(pm.latent(2, 16, 16, 24, 0.3)),
+        pm.layer(pm.latent(3, 8, 24, 24, 0.4, kv_from=1), pm.dense(32)),
+        pm.layer(pm.latent(1, 32, 8, 24, 0.2, kv_from=0))])
+    folder = pm.write(tmp_path / "m", raw, 12)
+    requests = [helpers.random_tokens(n, 120, 40 + n) for n in (90, 66, 5)]
+    for variant in range(2):
+        if variant:
+            files = ModelFiles(folder)
+            tensors = {n: files.read(n).clone() for n in files.names()}
+            files.close()
+            tensors["l1.mix.dkv"] = tensors["l1.mix.dkv"].flip(0).contiguous()
+            write_safetensors(tmp_path / "m" / "model.safetensors", tensors)
+        plain = pp.PlainPusunex(folder)
+        for dtype in ("float32", "bfloat16"):
+            eng = _engine(folder, dtype, max_tokens=512)
+            assert len(eng.cache.groups) == 1 and eng.cache.groups[0].entries == [0, 1]        # the readers keep nothing
+            for k, steps in {"batched": helpers.batched_steps(requests, [80, 60, 1], 3),
+                             "pieces": helpers.piece_steps(requests, [helpers.cut(len(r), [2, 31]) for r in requests], 1)}.items():
+                got = _run(eng, tmp_path / f"{variant}{dtype}{k}", steps, requests)
+                _compare(got, plain, requests, TOL[dtype], f"kv_from variant {variant} {dtype} {k}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_sizes(tmp_path, dtype):
+    """Latents of 128 and 96 + 32 at a width of 1,024, states of 64 x 128, experts of 256: in bfloat16 the prompts go
+    through the tensor-core products and the tensor-core attention over latents, decoding through the kernel that
+    splits the keys."""
+    folder = pm.write(tmp_path / "m", pm.REAL, 31, std=0.05)
+    plain = pp.PlainPusunex(folder)
+    lens = [333, 70, 200]
+    requests = [helpers.random_tokens(n, 1000, 800 + i) for i, n in enumerate(lens)]
+    eng = _engine(folder, dtype, max_tokens=2048)
+    runs = {"batched": helpers.batched_steps(requests, [n - 6 for n in lens], 3),
+            "pieces": helpers.piece_steps(requests, [helpers.cut(n, [150, 2, 100]) for n in lens], batch_size=1)}
+    for k, steps in runs.items():
+        got = _run(eng, tmp_path / k, steps, requests)
+        _compare(got, plain, requests, TOL[dtype], f"REAL {dtype} {k}")
+    short = [r[:9] for r in requests]
+    for k, steps in {"short_alone": helpers.tail_steps(short[:1], 1000),
+                     "short_batch": helpers.batched_steps(short, [1, 2, 3], 3)}.items():
+        reqs = short[:1] if k == "short_alone" else short
+        got = _run(eng, tmp_path / k, steps, reqs)
+        _compare(got, plain, reqs, TOL[dtype], f"REAL {dtype} {k}")
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_slots_and_pages_are_used_again(models, tmp_path, dtype):
+    """Two slots for six requests: a request that starts in a slot another left reads nothing of it, neither latents
+    nor the recurrent state."""
+    folder, plain = models["P1"]
+    vocab = plain.cfg["vocab"]
+    lens = [70, 40, 90, 66, 5, 120]
+    requests = [helpers.random_tokens(n, vocab, 500 + i) for i, n in enumerate(lens)]
+    eng = _engine(folder, dtype, max_tokens=256, n_slots=2)
+    steps = helpers.batched_steps(requests, [max(1, n - 8) for n in lens], 2)
+    got = _run(eng, tmp_path / "t", steps, requests)
+    _compare(got, plain, requests, TOL[dtype], f"reuse {dtype}")
+    assert eng.cache.slots.n_free == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_generate(models, dtype):
+    """Greedy generation through Engine.generate (scheduler, sampler, step ahead) against the plain model."""
+    from oracle_engine_b200 import GenParams
+    folder, plain = models["P2"]
+    vocab = plain.cfg["vocab"]
+    eng = _engine(folder, dtype)
+    prompts = [helpers.random_tokens(n, vocab, 40 + i) for i, n in enumerate((1, 9, 70))]
+    n_new = 150
+    got = eng.generate(prompts, GenParams.greedy(n_new, ignore_eos=True))
+    assert [len(g) for g in got] == [n_new] * 3
+    margin = 1e-3 if dtype == "float32" else 2 * TOL[dtype]
+    for p, g in zip(prompts, got):
+        lg = plain.logits(list(p) + list(g))
+        scale = float(lg.pow(2).mean().sqrt())
+        for j, tok in enumerate(g):
+            row = lg[len(p) + j - 1]
+            assert row.max().item() - row[tok].item() <= margin * max(1.0, scale), f"{dtype}: token {j} of a prompt of {len(p)}"
+    # a budget of prompt tokens per step: the 70-token prompt goes through in portions beside decoding rows
+    again = eng.generate(prompts, GenParams.greedy(12, ignore_eos=True), max_step_tokens=16)
+    if dtype == "float32":
+        assert again == [g[:12] for g in got]
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.n_slots
+
+
+def test_command_lines(models, tmp_path):
+    """bin/trace_run and bin/oracle load the design by its config.json."""
+    folder, plain = models["P3"]
+    vocab = plain.cfg["vocab"]
+    requests = [helpers.random_tokens(n, vocab, 900 + i) for i, n in enumerate((20, 66))]
+    steps = helpers.batched_steps(requests, [15, 60], 2)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        helpers.run_trace_cli(folder, dtype, steps, out, 256)
+        files = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
+        got = helpers.collect(steps, files, requests)
+        _compare(got, plain, requests, TOL[dtype], f"trace_run {dtype}")
+    prompt = requests[0][:12]
+    r = subprocess.run([sys.executable, str(helpers.ROOT / "bin" / "oracle"), "-m", folder, "--tokens",
+                        ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--dtype", "float32", "--ignore-eos"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == pp.generate(plain, prompt, 6)
