@@ -13,6 +13,10 @@
 // keys are read, so a windowed layer's cost does not grow with the context.
 // A step of single tokens may split a sequence's pages over `n_splits` CTAs (grid x): each writes its unnormalised
 // sums, maximum and denominator as float32, and attn_split_merge_kernel puts them together in split order.
+//
+// -DOE_KV_SHARED=1: the values are the first DV columns of the key rows (DV <= DK), one tensor [pages][KVH][64][DK]:
+// attention over a cache of latents, where a row [latent | shared key part] is the key of every head and its first
+// part the value (csrc/attention_latent.cu).  Only the key panel is staged; P V reads its first DV columns.
 #include "common.cuh"
 
 #ifndef OE_DK
@@ -21,14 +25,19 @@
 #ifndef OE_DV
 #define OE_DV 128
 #endif
+#ifndef OE_KV_SHARED
+#define OE_KV_SHARED 0
+#endif
 
 namespace {
 
 constexpr int DK = OE_DK, DV = OE_DV;
 constexpr int BN = OE_PAGE;
 constexpr int NWARPS = 4;
-constexpr int K_ROW = DK * 2 + 16, V_ROW = DV * 2 + 16;      // padded rows: ldmatrix without bank conflicts
-constexpr int K_TILE = BN * K_ROW, V_TILE = BN * V_ROW;
+constexpr bool KV_SHARED = OE_KV_SHARED != 0;
+constexpr int K_ROW = DK * 2 + 16, V_ROW = KV_SHARED ? K_ROW : DV * 2 + 16;      // padded rows: ldmatrix without bank conflicts
+constexpr int K_TILE = BN * K_ROW, V_TILE = KV_SHARED ? 0 : BN * V_ROW;
+static_assert(!KV_SHARED || DV <= DK, "shared rows: the values are the first DV columns of the keys");
 constexpr int KS = DK / 16;
 static_assert(DK % 16 == 0 && DK >= 16 && DK <= 256 && DV % 16 == 0 && DV >= 16 && DV <= 256, "head sizes: multiples of 16 up to 256");
 
@@ -37,7 +46,7 @@ struct Args {
     const bf16* q;             // rows of q_stride elements, head h at h*DK (rotated already)
     long long q_stride;
     const bf16* kcache;        // [pages][KVH][64][DK]
-    const bf16* vcache;        // [pages][KVH][64][DV]
+    const bf16* vcache;        // [pages][KVH][64][DV] (not read when the values are part of the key rows)
     const int* tables;         // [B, max_pages]
     int max_pages;
     const int* cu_q;
@@ -78,6 +87,7 @@ __device__ __forceinline__ void load_page(uint8_t* ks, uint8_t* vs, const Args& 
     const bf16* vg = a.vcache + ((size_t)page * a.KVH + kvh) * (size_t)(BN * DV);
     for (int c = threadIdx.x; c < BN * DK / 8; c += NWARPS * 32)
         cp_async16(ks + (c / (DK / 8)) * K_ROW + (c % (DK / 8)) * 16, kg + (size_t)c * 8);
+    if (KV_SHARED) return;
     for (int c = threadIdx.x; c < BN * DV / 8; c += NWARPS * 32)
         cp_async16(vs + (c / (DV / 8)) * V_ROW + (c % (DV / 8)) * 16, vg + (size_t)c * 8);
 }
@@ -151,7 +161,7 @@ attn_split_mma_kernel(const Args a) {
     for (int it = 0; it < n_blocks; it++) {
         const int j = j_lo + it;
         uint8_t* ks_cur = smem + (size_t)(it & 1) * (K_TILE + V_TILE);
-        uint8_t* vs_cur = ks_cur + K_TILE;
+        uint8_t* vs_cur = KV_SHARED ? ks_cur : ks_cur + K_TILE;
         if (it + 1 < n_blocks) {
             uint8_t* nxt = smem + (size_t)((it + 1) & 1) * (K_TILE + V_TILE);
             load_page(nxt, nxt + K_TILE, a, trow[j + 1], kvh);

@@ -109,8 +109,10 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     K = a.shape[1]
+    # the epilogues store 16 bytes at a time where an element's offset from `out` allows it, so `out` itself (a view
+    # into a wider buffer, for instance one head's columns) must start on a 16-byte boundary
     return (K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and w.is_contiguous()
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1 and out.data_ptr() % 16 == 0)
 
 
 SKINNY_MAX_TOKENS = 16      # up to here every product goes to the weight-streaming kernel (gemm_skinny.cu).  Alone, the

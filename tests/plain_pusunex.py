@@ -178,8 +178,16 @@ def token_side(x, tokens, w, i, dim, eps):
     return x + rms(y, eps) * w[f"l{i}.side.norm"]
 
 
-def forward(cfg, w, tokens, return_layers=False):
-    """One sequence from its first token; logits [T, vocab] (and the stream after every layer, before averaging)."""
+def router_gap(h, w, pre, mlp):
+    """Per token, how far the last chosen expert's router logit lies above the first one that is not chosen."""
+    z = (h @ w[pre + "router"].T).sort(-1, descending=True).values
+    top = mlp["router"]["top"]
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else torch.full((h.shape[0],), float("inf"), dtype=F64)
+
+
+def forward(cfg, w, tokens, return_layers=False, gaps=None):
+    """One sequence from its first token; logits [T, vocab] (and the stream after every layer, before averaging).
+    gaps: a list that receives every mixture layer's `router_gap`."""
     eps, groups = cfg["norm"]["eps"], cfg["norm"].get("groups") or 1
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
@@ -202,6 +210,8 @@ def forward(cfg, w, tokens, return_layers=False):
         if mlp is not None:
             h = group_norm(x, w[pre + "norm2"], eps, groups)
             y = dense_ffn(h, w, pre + "mlp.", eps) if mlp["kind"] == "dense" else moe_ffn(h, w, pre + "mlp.", mlp)
+            if gaps is not None and mlp["kind"] == "moe":
+                gaps.append(router_gap(h, w, pre + "mlp.", mlp))
             x = x + group_norm(y, w[pre + "norm2b"], eps, groups)
         if side:
             x = token_side(x, tokens, w, i, side["dim"], eps)
@@ -226,6 +236,15 @@ class PlainPusunex:
 
     def logits(self, tokens):
         return forward(self.cfg, self.w, tokens)
+
+    def close_calls(self, tokens, margin):
+        """The positions at which some router's choice hangs on less than `margin` of a logit: arithmetic of fewer
+        bits may choose otherwise there, and no comparison at reduced precision should rest on them."""
+        gaps = []
+        forward(self.cfg, self.w, tokens, gaps=gaps)
+        if not gaps:
+            return set()
+        return set(torch.nonzero(torch.stack(gaps).min(0).values < margin).flatten().tolist())
 
     def layers(self, tokens):
         """The stream that leaves every layer (after the depth average), [layers, T, D]."""

@@ -80,6 +80,13 @@ REAL = config(1000, 1024, 1e-6, 4, 32, [
 ALL = {"P1": (P1, 3), "P2": (P2, 4), "P3": (P3, 5), "SHARP": (SHARP, 6), "LONG_MEMORY": (LONG_MEMORY, 8)}
 
 
+# In bfloat16 a router now and then chooses another expert than exact arithmetic does (two scores a rounding apart).
+# The norm after the feed-forward gives the experts' output the stream's own size, so one such token would be half
+# wrong, and every later token that attends to it a little.  The tests' mixtures add a quarter of that: the other
+# choice still shows at its own position, which a comparison in bfloat16 leaves out, and no longer at the later ones.
+MOE_OUT = 0.25
+
+
 def write(folder, raw, seed, std=0.1, decay_bias=3.0):
     """A model folder of seeded random weights, adjusted as the top of this file says."""
     from oracle_engine_b200.config.pusunex import PusunexConfig
@@ -88,7 +95,7 @@ def write(folder, raw, seed, std=0.1, decay_bias=3.0):
     folder = Path(folder)
     write_model_folder(folder, PusunexConfig.from_dict(raw), seed=seed, std=std)
     files = ModelFiles(folder)
-    tensors = {}
+    tensors, names = {}, set(files.names())
     for n in files.names():
         t = files.read(n).clone()
         f = t.float()
@@ -100,6 +107,8 @@ def write(folder, raw, seed, std=0.1, decay_bias=3.0):
             f = f / f.numel()                     # a weighted mean, not a sum that grows with the depth
         elif n.endswith(".side.embed"):
             f = f * 5.0
+        elif n.endswith(".norm2b") and n[:-len("norm2b")] + "mlp.router" in names:
+            f = f * MOE_OUT                       # see MOE_OUT
         tensors[n] = f.to(t.dtype)
     files.close()
     write_safetensors(folder / "model.safetensors", tensors)
