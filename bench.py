@@ -6,7 +6,7 @@
     python bench.py --shape 8b --workload baseline      # 32 prompts of 128..4,096 tokens, 256 steps
     python bench.py --profile [--batch 64]              # device time per kind of kernel, on standard error
     python bench.py --impl reference --steps K          # the reference's own benchmark program (CPU)
-    python bench.py --design fuvipel|fovirax [--widths 1024,2048,3072] [--profile]
+    python bench.py --design fuvipel|fovirax|pusunex [--beside llama,fovirax] [--widths 1024,2048,3072] [--profile]
                                                         # that design beside a Llama of equal width and depth
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default
@@ -390,6 +390,35 @@ def fovirax_shape(width: int, layers: int, vocab: int) -> dict:
             "layers": [layer] * layers}
 
 
+def pusunex_shape(width: int, layers: int, vocab: int) -> dict:
+    """A Pusunex of real layer sizes, four kinds of layer in turn: attention over a latent of 256 with an output gate
+    and a PolyNorm feed-forward of 4 x width; gated linear attention with states of 64 x 128; attention over a latent
+    of 192 and a turned key part of 64 with a query latent of width / 2; attention that reads the first kind's
+    latents.  Heads of 128.  The last three carry Fovirax's mixture (8 experts of 2/3 x width, two chosen, a shared
+    expert of 4/3 x width).  Norms in 4 groups, a token side input of 64 columns per layer."""
+    heads = width // 128
+    ff = (2 * width // 3 + 63) // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 8, "top": 2}, "shared": {"ff": 2 * ff}}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            lay = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 4 * width},
+                   "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 256, "scale": 128 ** -0.5}}
+        elif kind == 1:
+            lay = {"type": "gla", "mlp": moe, "mixer": {"heads": heads, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}}
+        elif kind == 2:
+            lay = {"type": "latent_attention_2", "mlp": moe,
+                   "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": width // 2,
+                             "scale": 192 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}}
+        else:
+            lay = {"type": "latent_attention", "mlp": moe,
+                   "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 256, "scale": 128 ** -0.5, "kv_from": i - 3}}
+        out.append(lay)
+    return {"architecture": "Pusunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "token_side": {"dim": 64}, "layers": out}
+
+
 def llama_shape(width: int, layers: int, vocab: int) -> dict:
     """The Llama decoder of the same width, depth and vocabulary: heads of 128, four query heads to a key head,
     a SwiGLU of 8/3 x width (the same weights as a two-matrix feed-forward of 4 x width)."""
@@ -400,22 +429,31 @@ def llama_shape(width: int, layers: int, vocab: int) -> dict:
 
 
 def design_compare(args) -> int:
-    """Prefill and decode throughput of a design (--design) beside the Llama decoder at equal width, depth and
-    vocabulary (random weights), one JSON line; with --profile the device time per kind of kernel instead."""
+    """Prefill and decode throughput of a design (--design) beside others (--beside, the Llama decoder unless
+    said otherwise) at equal width, depth and vocabulary (random weights), one JSON line; with --profile the device
+    time per kind of kernel instead."""
     import torch
     from oracle_engine_b200 import LlamaConfig
     from oracle_engine_b200.config.fovirax import FoviraxConfig
     from oracle_engine_b200.config.fuvipel import FuvipelConfig
+    from oracle_engine_b200.config.pusunex import PusunexConfig
     from oracle_engine_b200.engine.engine import Engine
-    design = {"fuvipel": lambda *a: FuvipelConfig.from_dict(fuvipel_shape(*a)),
-              "fovirax": lambda *a: FoviraxConfig.from_dict(fovirax_shape(*a))}[args.design]
+    designs = {"fuvipel": lambda *a: FuvipelConfig.from_dict(fuvipel_shape(*a)),
+               "fovirax": lambda *a: FoviraxConfig.from_dict(fovirax_shape(*a)),
+               "pusunex": lambda *a: PusunexConfig.from_dict(pusunex_shape(*a)),
+               "llama": lambda *a: LlamaConfig.from_dict(llama_shape(*a))}
+    beside = [b for b in (args.beside or "llama").split(",") if b and b != args.design]
+    unknown = [b for b in beside if b not in designs]
+    if unknown:
+        print(json.dumps({"error": f"--beside {unknown[0]}: not one of {sorted(designs)}"}))
+        return 2
     pk = peaks()
     layers, vocab, context = args.layers or 8, 32000, 1024
     sizes = {}
     for width in [int(w) for w in args.widths.split(",")]:
         row = {}
-        for name, cfg in ((args.design, design(width, layers, vocab)),
-                          ("llama", LlamaConfig.from_dict(llama_shape(width, layers, vocab)))):
+        for name in [args.design] + beside:
+            cfg = designs[name](width, layers, vocab)
             engine = Engine.from_config(cfg, seed=SEED, dtype=args.dtype, max_tokens=64 * context + 4096,
                                         max_seq_len=4096, n_slots=64)
             if args.profile:
@@ -443,7 +481,7 @@ def design_compare(args) -> int:
             torch.cuda.empty_cache()
         sizes[str(width)] = row
     if not args.profile:
-        print(json.dumps({"design": f"{args.design} beside llama at equal width, depth and vocabulary", "layers": layers,
+        print(json.dumps({"design": f"{args.design} beside {' and '.join(beside)} at equal width, depth and vocabulary", "layers": layers,
                           "vocab": vocab, "dtype": args.dtype, "prefill_tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
                           "peaks": pk, "data": "synthetic token ids, random-init weights N(0, 0.02) from seed 2",
                           "sizes": sizes}))
@@ -562,8 +600,9 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
-    ap.add_argument("--design", default=None, choices=["fuvipel", "fovirax"],
+    ap.add_argument("--design", default=None, choices=["fuvipel", "fovirax", "pusunex"],
                     help="measure this design beside the Llama decoder at equal sizes instead of the headline workload")
+    ap.add_argument("--beside", default=None, help="the designs to measure beside --design, comma-separated (default llama)")
     ap.add_argument("--widths", default="1024,2048,3072", help="model widths of --design")
     args = ap.parse_args()
 

@@ -580,15 +580,19 @@ def attention_split_supported(dk: int, dv: int, n_heads: int, n_kv_heads: int) -
 _split_libs: dict = {}
 
 
-def _attn_split_lib(dk: int, dv: int):
-    fn = _split_libs.get((dk, dv))
+def _attn_split_lib(dk: int, dv: int, shared: bool = False):
+    """shared: the values are the first dv columns of the key rows (one tensor in the cache)."""
+    fn = _split_libs.get((dk, dv, shared))
     if fn is None:
-        lib = _build.load("attention_split_tc", defines={"OE_DK": dk, "OE_DV": dv})
+        defines = {"OE_DK": dk, "OE_DV": dv}
+        if shared:
+            defines["OE_KV_SHARED"] = 1
+        lib = _build.load("attention_split_tc", defines=defines)
         fn = lib.oe_attn_split_mma
         fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p]
         fn.restype = c_int
-        _split_libs[(dk, dv)] = fn
+        _split_libs[(dk, dv, shared)] = fn
     return fn
 
 
@@ -596,16 +600,22 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
                     scale: float, cap: float) -> None:
     """out[t] = attention of token t's query heads over the keys (pos - window, pos] of its sequence, scores capped
     by cap tanh(s / cap) when cap > 0; bfloat16, q rotated already (rows of q may be a view of the fused product),
-    kcache [pages, G, PAGE, dk], vcache [pages, G, PAGE, dv]."""
+    kcache [pages, G, PAGE, dk], vcache [pages, G, PAGE, dv]; vcache None: the values are the first dv columns of the
+    key rows."""
     from .ops import PAGE
+    shared = vcache is None
+    if shared:
+        if dv > dk:
+            raise ops.KernelError("attention_split: values taken from the key rows cannot be longer than the keys")
+        vcache = kcache
     if out.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 \
             or vcache.dtype != torch.bfloat16:
         raise ops.KernelError("attention_split: bfloat16 tensors expected")
     if not out.is_contiguous() or out.shape[1] != n_heads * dv or q.stride(1) != 1 or q.shape[1] < n_heads * dk \
             or q.stride(0) % 2 or q.data_ptr() % 4:
         raise ops.KernelError("attention_split: out contiguous [T, H dv]; q rows of at least H dk values, 4-byte aligned")
-    if tuple(kcache.shape[1:]) != (n_kv_heads, PAGE, dk) or tuple(vcache.shape[1:]) != (n_kv_heads, PAGE, dv) \
-            or not (kcache.is_contiguous() and vcache.is_contiguous()):
+    if tuple(kcache.shape[1:]) != (n_kv_heads, PAGE, dk) or not (kcache.is_contiguous() and vcache.is_contiguous()) \
+            or (not shared and tuple(vcache.shape[1:]) != (n_kv_heads, PAGE, dv)):
         raise ops.KernelError("attention_split: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv]")
     # A step of single tokens: a sequence's pages are split over CTAs while the (sequence, KV head) pairs alone
     # would leave SMs idle; the partial sums go through float32 scratch and a merge kernel.
@@ -615,7 +625,7 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
         n_splits = max(1, min(keys // PAGE + 1, (2 * _sm_count()) // max(1, ctx.n_seqs * n_kv_heads), 32))
         if n_splits > 1:
             partial = torch.empty(ctx.n_seqs * n_heads * n_splits * (dv + 2), dtype=torch.float32, device=out.device)
-    code = _attn_split_lib(dk, dv)(out.data_ptr(), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+    code = _attn_split_lib(dk, dv, shared)(out.data_ptr(), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                    tables.data_ptr(), tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(),
                                    ctx.seq_qlen.data_ptr(), ctx.n_seqs, int(ctx.max_qlen), n_heads, n_kv_heads, int(window),
                                    float(scale), float(cap or 0.0), n_splits,
@@ -628,5 +638,13 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
 # ---------------------------------------------------------------------------------------- a cache of latents
 
 def attention_latent_supported(n_heads: int, r: int, rd: int) -> bool:
-    """Whether a tensor-core kernel takes the attention over latent rows [r + rd] (parts/latent_attention.py)."""
-    return False
+    """Whether the tensor-core kernel takes the attention over latent rows [r + rd] (parts/latent_attention.py): one
+    key head of r + rd values whose first r are also the value, read by all the query heads."""
+    return r % 16 == 0 and attention_split_supported(r + rd, r, n_heads, 1)
+
+
+def attention_latent(out, qfull, rows, tables, ctx, n_heads: int, r: int, rd: int, scale: float) -> None:
+    """out[t, h, :r] = sum_j p_j rows[j, :r] with p = softmax_j<=t(scale * qfull[t, h] . rows[j]); qfull [T, H (r + rd)]
+    (the queries taken through the key projection, the turned part behind), rows [pages, PAGE, r + rd]."""
+    attention_split(out, qfull, rows.view(rows.shape[0], 1, rows.shape[1], r + rd), None, tables, ctx, n_heads, 1,
+                    r + rd, r, 0, scale, 0.0)
