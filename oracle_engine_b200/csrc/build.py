@@ -48,6 +48,7 @@ LIBRARIES = {
     "attention_tc": ("attention_mma.cu", []),
     "attention_tc5": ("attention_tcgen05.cu", []),
     "attention_split_tc": ("attention_split_mma.cu", []),
+    "head_matmul_tc": ("head_matmul_mma.cu", []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -175,6 +176,7 @@ def build_all(names=None, verbose: bool = True) -> list[Path]:
             jobs.extend((n, {"OE_HD": hd}) for hd in (64, 128))
         elif n == "attention_split_tc":
             jobs.extend((n, {"OE_DK": dk, "OE_DV": dv}) for dk, dv in ((64, 128), (128, 128)))
+            jobs.append((n, {"OE_DK": 256, "OE_DV": 192, "OE_KV_SHARED": 1}))
         else:
             jobs.append((n, None))
     results: dict[object, object] = {}

@@ -648,3 +648,34 @@ def attention_latent(out, qfull, rows, tables, ctx, n_heads: int, r: int, rd: in
     (the queries taken through the key projection, the turned part behind), rows [pages, PAGE, r + rd]."""
     attention_split(out, qfull, rows.view(rows.shape[0], 1, rows.shape[1], r + rd), None, tables, ctx, n_heads, 1,
                     r + rd, r, 0, scale, 0.0)
+
+
+def head_matmul_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel (csrc/head_matmul_mma.cu) takes out[t, h] = w[h] @ a[t, h]: bfloat16 operands whose
+    rows start on 16-byte boundaries, a shared size that is a multiple of 16."""
+    K = a.shape[2]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and K % 16 == 0 and a.stride(0) % 8 == 0 and a.stride(1) % 8 == 0 and a.stride(2) == 1 and out.stride(2) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def head_matmul(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[t, h, :] = w[h] @ a[t, h, :] for all heads in one launch: a [T, H, K], out [T, H, N] (views), w [H, N, K]."""
+    T, H, K = a.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (H, N, K) or tuple(out.shape) != (T, H, N) or not head_matmul_supported(a, w, out):
+        raise ops.KernelError("head_matmul: a [T, H, K], w [H, N, K] bfloat16 with K a multiple of 16, out [T, H, N]")
+    key = "head_matmul"
+    fns = _state.get(key)
+    if fns is None:
+        lib = _build.load("head_matmul_tc")
+        fns = {}
+        for name, dt in (("oe_head_matmul_mma_bf16", torch.bfloat16), ("oe_head_matmul_mma_f32", torch.float32)):
+            fn = getattr(lib, name)
+            fn.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int,
+                           c_int, c_void_p]
+            fn.restype = c_int
+            fns[dt] = fn
+        _state[key] = fns
+    ops._check(fns[out.dtype](out.data_ptr(), out.stride(0), out.stride(1), a.data_ptr(), a.stride(0), a.stride(1),
+                              w.data_ptr(), T, H, N, K, ops._stream()), "head_matmul_mma")

@@ -128,12 +128,18 @@ class LatentAttention(Part):
         return self.w.get("in") if self.w.get("in") is not None else self.w.get("q")
 
     def _per_head(self, out, a, w):
-        """out[:, h, :] = w[h] @ a[:, h, :]; one launch for a handful of tokens on the bfloat16 path, else a product per
-        head (float32: the CUDA-core product whose sums do not depend on the batch)."""
+        """out[:, h, :] = w[h] @ a[:, h, :].  bfloat16: one launch for all heads, a kernel that streams the weights once
+        for a handful of tokens, the tensor cores for more; else a product per head (float32: the CUDA-core product
+        whose sums do not depend on the batch)."""
         T = a.shape[0]
         if self.rt.dtype == torch.bfloat16 and T <= HEAD_MATMUL_MAX_TOKENS:
             ops.head_matmul(out, a, w)
             return
+        if self.rt.dtype == torch.bfloat16 and self.rt.tensor_cores:
+            from ..csrc import ops_tc
+            if ops_tc.head_matmul_supported(a, w, out):
+                ops_tc.head_matmul(out, a, w)
+                return
         for h in range(self.H):
             matmul_nt(self.rt, out[:, h, :], a[:, h, :], w[h])
 

@@ -637,3 +637,24 @@ def test_gemm_wait_that_runs_out_returns_and_reports():
         ops_tc.gemm(good, a, w, kernel="tcgen05", split_k=False)
         assert (good.double() - want).abs().max() < 2e-6 * K + 1e-5
     assert ops_tc.device_error() == 0
+
+
+@pytest.mark.parametrize("T,H,N,K", [(1, 1, 8, 16), (70, 3, 40, 48), (64, 2, 64, 64), (257, 5, 130, 208), (17, 16, 256, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_head_matmul_tensor_cores(T, H, N, K, out_dtype):
+    """out[t, h] = w[h] @ a[t, h] with a and out views into wider rows (a head's columns among others): tails in
+    tokens, outputs and the shared size, one token, one head."""
+    from oracle_engine_b200.csrc import ops_tc
+    wide_a = _rand(T, H * (K + 8), dtype=torch.bfloat16, seed=1)
+    a = wide_a.view(T, H, K + 8)[:, :, :K]
+    w = _rand(H, N, K, dtype=torch.bfloat16, scale=K ** -0.5, seed=2)
+    wide_o = torch.full((T, H * (N + 3)), 7.0, dtype=out_dtype, device=DEV)
+    out = wide_o.view(T, H, N + 3)[:, :, :N]
+    assert ops_tc.head_matmul_supported(a, w, out)
+    ops_tc.head_matmul(out, a, w)
+    torch.cuda.synchronize()
+    want = torch.einsum("thk,hnk->thn", a.double(), w.double())
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 1e-4
+    assert (out.double() - want).abs().max().item() < tol * max(1.0, want.abs().max().item())
+    assert (wide_o.view(T, H, N + 3)[:, :, N:] == 7.0).all()                  # nothing beyond a head's outputs
+    assert not ops_tc.head_matmul_supported(wide_a.view(T, H, K + 8)[:, :, 1:K + 1], w, out)      # rows off a 16-byte boundary
