@@ -75,6 +75,7 @@ _SIGNATURES = {
     },
     "gla": {
         "oe_gla_scan": [_P, _P, _P, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+        "oe_gla_scan_segments": [_P, _P, _P, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P, _P],
     },
     "attention_latent": {
         "oe_latent_write": [_P, _L, _P, _F, _P, _L, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -619,10 +620,13 @@ def depth_average(x: torch.Tensor, hist: torch.Tensor, w: torch.Tensor, n: int) 
 # ---------------------------------------------------------------------------------------- gla.cu
 
 def gla_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: int, off_k: int, off_v: int, z: torch.Tensor,
-             bias: torch.Tensor, ctx, heads: int, dk: int, dv: int, q_scale: float, tau: float) -> None:
+             bias: torch.Tensor, ctx, heads: int, dk: int, dv: int, q_scale: float, tau: float, segments=None) -> None:
     """Per sequence and head, over the step's tokens in order: alpha = sigmoid(z + bias)^(1/tau) [dk];
     S <- diag(alpha) S + k v^T; o = S^T (q * q_scale).  proj float32 rows holding q, k (heads*dk) and v (heads*dv) at
-    the given column offsets; z float32 [T, heads*dk]; state float32 [slots, heads, dk, dv]; o float32 [T, heads*dv]."""
+    the given column offsets; z float32 [T, heads*dk]; state float32 [slots, heads, dk, dv]; o float32 [T, heads*dv].
+    segments (seg_len, n_seg, seg_state, seg_decay): every sequence's tokens (at most seg_len * n_seg) run as segments
+    side by side; the scratch tensors are float32 [n_seqs, n_seg, heads, dk, dv] and [n_seqs, n_seg, heads, dk].  The
+    result differs from the one walk by the order of the sums only."""
     _dev(o, state, proj, z, bias)
     for t, n in ((o, "o"), (state, "state"), (bias, "bias")):
         _f32c(t, n)
@@ -634,6 +638,20 @@ def gla_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: in
         raise KernelError("gla_scan: shapes do not agree")
     e = proj.element_size()
     base = proj.data_ptr()
+    if segments is not None:
+        seg_len, n_seg, seg_state, seg_decay = segments
+        _dev(seg_state, seg_decay)
+        _f32c(seg_state, "seg_state")
+        _f32c(seg_decay, "seg_decay")
+        if seg_len < 1 or n_seg < 1 or seg_len * n_seg < int(ctx.max_qlen) \
+                or seg_state.numel() < ctx.n_seqs * n_seg * heads * dk * dv or seg_decay.numel() < ctx.n_seqs * n_seg * heads * dk:
+            raise KernelError("gla_scan: the segments do not cover the step's longest sequence, or their scratch is too small")
+        _check(_fn("gla", "oe_gla_scan_segments")(
+            _ptr(o), _ptr(state), base + off_q * e, base + off_k * e, base + off_v * e, proj.stride(0), _ptr(z), z.stride(0),
+            _ptr(bias), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), ctx.n_seqs, heads, dk, dv, float(q_scale), 1.0 / float(tau),
+            int(seg_len), int(n_seg), _ptr(seg_state), _ptr(seg_decay), _stream()), "gla_scan_segments")
+        LAUNCHES[0] += 2
+        return
     _check(_fn("gla", "oe_gla_scan")(_ptr(o), _ptr(state), base + off_q * e, base + off_k * e, base + off_v * e,
                                      proj.stride(0), _ptr(z), z.stride(0), _ptr(bias), _ptr(ctx.seq_slot), _ptr(ctx.cu_q),
                                      ctx.n_seqs, heads, dk, dv, float(q_scale), 1.0 / float(tau), _stream()), "gla_scan")

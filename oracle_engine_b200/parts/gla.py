@@ -21,6 +21,11 @@ from .spec import StateNeed, TensorDecl
 _NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2_bias": "a2.b"}
 
 
+SEGMENTS_FROM = 256         # a step whose longest sequence brings this many tokens runs them as segments side by side
+SEGMENT_MIN = 32            # tokens of the shortest segment
+SEGMENT_BLOCKS = 2368       # blocks of the scan that keep the GPU busy (16 per SM)
+
+
 @MIXERS.register("gated_linear_attention")
 class GatedLinearAttention(Part):
     graph_safe = True
@@ -81,6 +86,23 @@ class GatedLinearAttention(Part):
     def first_weights(self):
         return self.w_in
 
+    def _segments(self, ctx):
+        """How a step with long prompts cuts its sequences into segments that run side by side (csrc/gla.cu), or None
+        for the one walk.  float32 serving keeps the one walk: there a position's logits are the same bits under
+        every cut of the prompt into steps."""
+        longest = int(ctx.max_qlen)
+        if self.rt.dtype != torch.bfloat16 or longest < SEGMENTS_FROM or torch.cuda.is_current_stream_capturing():
+            return None             # (a captured step's longest sequence is a bound, not a length)
+        pairs = -(-SEGMENT_BLOCKS // (self.H * -(-self.dv // 32)))         # (sequence, segment) pairs that fill the GPU
+        n_seg = max(1, min(-(-pairs // max(1, ctx.n_seqs)), longest // SEGMENT_MIN))
+        seg_len = -(-(-(-longest // n_seg)) // 8) * 8
+        n_seg = -(-longest // seg_len)
+        if n_seg < 2:
+            return None
+        seg_state = self.rt.buffer("gla.seg_state", ctx.n_seqs * n_seg, self.H, self.dk * self.dv, dtype=torch.float32)
+        seg_decay = self.rt.buffer("gla.seg_decay", ctx.n_seqs * n_seg, self.H, self.dk, dtype=torch.float32)
+        return seg_len, n_seg, seg_state, seg_decay
+
     def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32, buf = h.shape[0], torch.float32, self.rt.buffer
@@ -93,7 +115,7 @@ class GatedLinearAttention(Part):
         matmul_nt(self.rt, z, low, self.w_a2)
         o = buf("gla.o", T, vv, dtype=f32)
         ops.gla_scan(o, state["S"], proj, 0, qk, 2 * qk, z, self.bias, ctx, self.H, self.dk, self.dv, self.dk ** -0.5,
-                     self.tau)
+                     self.tau, segments=self._segments(ctx))
         y = buf("gla.y", T, vv)
         ops.head_gate(y, o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm_w, self.H, self.dv, True, "silu", self.eps)
         matmul_nt(self.rt, residual, y, self.w_o, accumulate=not overwrite)

@@ -251,6 +251,53 @@ def test_real_sizes(tmp_path, dtype):
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("H,dk,dv,seg_len,lens", [(2, 16, 40, 8, [100, 3, 17, 64, 0]), (3, 40, 32, 24, [300, 49, 48]),
+                                                   (1, 64, 128, 128, [1000, 129, 128, 127])])
+def test_linear_attention_in_segments(H, dk, dv, seg_len, lens):
+    """The scan that runs a sequence's tokens as segments side by side, against the recurrence token by token in
+    float64: sequences that end at a segment's edge, one token before and after it, shorter than one segment and
+    empty; entering states that are not zero; decays from nearly 0 to nearly 1."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(H * 1000 + dk)
+    T, B, tau = sum(lens), len(lens), 4.0
+    qk, vv = H * dk, H * dv
+    proj = torch.randn(T, 2 * qk + vv + 5, generator=g)
+    z = torch.randn(T, qk, generator=g) * 3
+    bias = torch.randn(qk, generator=g) + 2
+    slots = [B - 1 - b for b in range(B)]
+    state0 = torch.randn(B + 1, H, dk, dv, generator=g)
+    alpha = (torch.sigmoid(z.double() + bias.double()) ** (1 / tau)).reshape(T, H, dk)
+    want_o, want_s = torch.zeros(T, H, dv, dtype=torch.float64), state0.double().clone()
+    cu = [0]
+    for b, n in enumerate(lens):
+        S = want_s[slots[b]].clone()
+        for t in range(cu[-1], cu[-1] + n):
+            q, k = (proj[t, i * qk:(i + 1) * qk].double().reshape(H, dk) for i in (0, 1))
+            v = proj[t, 2 * qk:2 * qk + vv].double().reshape(H, dv)
+            S = alpha[t].unsqueeze(-1) * S + k.unsqueeze(-1) * v.unsqueeze(-2)
+            want_o[t] = torch.einsum("hkv,hk->hv", S, q * dk ** -0.5)
+        want_s[slots[b]] = S
+        cu.append(cu[-1] + n)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)            # noqa: E731
+    n_seg = -(-max(lens) // seg_len)
+    ctx = SimpleNamespace(seq_slot=i32(slots), cu_q=i32(cu), n_seqs=B, max_qlen=max(lens))
+    scale = float(want_o.abs().max())
+    for segments in (None, (seg_len, n_seg, torch.full((B * n_seg, H, dk * dv), 9.0, device=dev),
+                            torch.full((B * n_seg, H, dk), 9.0, device=dev))):
+        o = torch.full((T, vv), 7.0, device=dev)
+        state = state0.to(dev).clone()
+        ops.gla_scan(o, state, proj.to(dev), 0, qk, 2 * qk, z.to(dev), bias.to(dev), ctx, H, dk, dv, dk ** -0.5, tau,
+                     segments=segments)
+        what = "one walk" if segments is None else "segments"
+        assert (o.double().cpu().reshape(T, H, dv) - want_o).abs().max().item() < 2e-5 * scale, what
+        assert (state.double().cpu() - want_s).abs().max().item() < 2e-5 * float(want_s.abs().max()), what
+    with pytest.raises(Exception):
+        ops.gla_scan(o, state, proj.to(dev), 0, qk, 2 * qk, z.to(dev), bias.to(dev), ctx, H, dk, dv, dk ** -0.5, tau,
+                     segments=(seg_len, n_seg - 1, segments[2], segments[3]))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_slots_and_pages_are_used_again(models, tmp_path, dtype):
     """Two slots for six requests: a request that starts in a slot another left reads nothing of it, neither latents
