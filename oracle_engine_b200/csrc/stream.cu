@@ -15,8 +15,21 @@
 
 namespace {
 
-// One block per row; warp g takes the parts g, g + warps, ... : a part's sum is one warp's sum.
-template <typename T>
+// One block per row; warp g takes the parts g, g + warps, ... : a part's sum is one warp's sum.  VEC: the part's size is
+// a multiple of 4 and every row starts on a 16-byte boundary, so a lane moves 4 values at a time (a lane's sum then runs
+// over the values 4 lane + {0..3}, 4 (lane + 32) + {0..3}, ...: another fixed order, chosen by the sizes alone).
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 group_rmsnorm_kernel(T* y, const float* x, long long ldx, const float* __restrict__ w, int D, int groups, float eps) {
     pdl_launch_dependents();
@@ -28,6 +41,21 @@ group_rmsnorm_kernel(T* y, const float* x, long long ldx, const float* __restric
     for (int g = warp; g < groups; g += nw) {
         const float* xp = xr + (size_t)g * gs;
         float ss = 0.f;
+        if (VEC) {
+            const float4* xp4 = reinterpret_cast<const float4*>(xp);
+            const float4* w4 = reinterpret_cast<const float4*>(w + (size_t)g * gs);
+            for (int d = lane; d < gs / 4; d += 32) {
+                const float4 v = xp4[d];
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            const float s = 1.f / sqrtf(ss / (float)gs + eps);
+            for (int d = lane; d < gs / 4; d += 32) {
+                const float4 v = xp4[d], ww = w4[d];
+                store4(yr + (size_t)g * gs + 4 * d, (v.x * s) * ww.x, (v.y * s) * ww.y, (v.z * s) * ww.z, (v.w * s) * ww.w);
+            }
+            continue;
+        }
         for (int d = lane; d < gs; d += 32) { const float v = xp[d]; ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
         const float s = 1.f / sqrtf(ss / (float)gs + eps);
@@ -35,6 +63,7 @@ group_rmsnorm_kernel(T* y, const float* x, long long ldx, const float* __restric
     }
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 group_rmsnorm_add_kernel(float* dst, const float* y, const float* __restrict__ w, int D, int groups, float eps,
                          float coef, int accumulate, bf16* cast) {
@@ -47,6 +76,29 @@ group_rmsnorm_add_kernel(float* dst, const float* y, const float* __restrict__ w
     for (int g = warp; g < groups; g += nw) {
         const float* yp = yr + (size_t)g * gs;
         float ss = 0.f;
+        if (VEC) {
+            const float4* yp4 = reinterpret_cast<const float4*>(yp);
+            const float4* w4 = reinterpret_cast<const float4*>(w + (size_t)g * gs);
+            for (int d = lane; d < gs / 4; d += 32) {
+                const float4 v = yp4[d];
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            const float s = 1.f / sqrtf(ss / (float)gs + eps);
+            for (int d = lane; d < gs / 4; d += 32) {
+                const size_t at = (size_t)g * gs + 4 * d;
+                const float4 v = yp4[d], ww = w4[d];
+                float4 r = make_float4(coef * ((v.x * s) * ww.x), coef * ((v.y * s) * ww.y), coef * ((v.z * s) * ww.z),
+                                       coef * ((v.w * s) * ww.w));
+                if (accumulate) {
+                    const float4 old = *reinterpret_cast<const float4*>(dr + at);
+                    r.x = old.x + r.x; r.y = old.y + r.y; r.z = old.z + r.z; r.w = old.w + r.w;
+                }
+                *reinterpret_cast<float4*>(dr + at) = r;
+                if (cast) store4(cast + (size_t)blockIdx.x * D + at, r.x, r.y, r.z, r.w);
+            }
+            continue;
+        }
         for (int d = lane; d < gs; d += 32) { const float v = yp[d]; ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
         const float s = 1.f / sqrtf(ss / (float)gs + eps);
@@ -131,21 +183,33 @@ unsigned blocks_for(size_t total) {
 
 extern "C" {
 
+// whether every row of a [rows, D] tensor with row stride ld (values) and every part of it starts on a 16-byte boundary
+static bool rows_of_4(const void* p, long long ld, int D, int groups) {
+    return (D / groups) % 4 == 0 && ld % 4 == 0 && (uintptr_t)p % 16 == 0;
+}
+
 int oe_group_rmsnorm_f32(float* y, const float* x, long long ldx, const float* w, int rows, int D, int groups, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (groups < 1 || D < 1 || D % groups) return OE_ERR_UNSUPPORTED;
-    return oe_launch(group_rmsnorm_kernel<float>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
+    if (rows_of_4(x, ldx, D, groups) && rows_of_4(y, D, D, groups) && rows_of_4(w, D, D, groups))
+        return oe_launch(group_rmsnorm_kernel<float, true>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
+    return oe_launch(group_rmsnorm_kernel<float, false>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
 }
 int oe_group_rmsnorm_bf16(bf16* y, const float* x, long long ldx, const float* w, int rows, int D, int groups, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (groups < 1 || D < 1 || D % groups) return OE_ERR_UNSUPPORTED;
-    return oe_launch(group_rmsnorm_kernel<bf16>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
+    if (rows_of_4(x, ldx, D, groups) && (uintptr_t)y % 8 == 0 && rows_of_4(w, D, D, groups))
+        return oe_launch(group_rmsnorm_kernel<bf16, true>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
+    return oe_launch(group_rmsnorm_kernel<bf16, false>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, y, x, ldx, w, D, groups, eps);
 }
 int oe_group_rmsnorm_add(float* dst, const float* y, const float* w, int rows, int D, int groups, float eps, float coef,
                          int accumulate, bf16* cast, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (groups < 1 || D < 1 || D % groups) return OE_ERR_UNSUPPORTED;
-    return oe_launch(group_rmsnorm_add_kernel, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, dst, y, w, D, groups, eps, coef,
+    if (rows_of_4(dst, D, D, groups) && rows_of_4(y, D, D, groups) && rows_of_4(w, D, D, groups) && (uintptr_t)cast % 8 == 0)
+        return oe_launch(group_rmsnorm_add_kernel<true>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, dst, y, w, D, groups, eps,
+                         coef, accumulate, cast);
+    return oe_launch(group_rmsnorm_add_kernel<false>, dim3(rows), dim3(groups >= 8 ? 256 : 128), 0, st, dst, y, w, D, groups, eps, coef,
                      accumulate, cast);
 }
 int oe_poly_norm_f32(float* out, const float* z, long long ldz, const float* coef, int rows, int F, float eps, cudaStream_t st) {
