@@ -11,7 +11,8 @@
 //                         is 0); online softmax in float32 over chunks of 32 keys at absolute multiples of 32,
 //                         so a token's result does not depend on how the step was cut or batched.  The
 //                         32-bit path's attention, and the bfloat16 path's for head sizes that the tensor-core
-//                         kernel (attention_split_mma.cu) does not take.
+//                         kernel (attention_split_mma.cu) does not take.  `sinks` (null, or one float32 per query
+//                         head): the softmax's denominator also holds exp(sinks[h]), a term without key or value.
 #include "common.cuh"
 
 namespace {
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_split_kernel(T* out, const T* q, long long q_stride, const T* kcache, const T* vcache,
                   const int* __restrict__ tables, int max_pages, const int* __restrict__ tok_seq,
                   const int* __restrict__ tok_pos, int n_tokens, int H, int G, int dk, int dv, int window, float scale,
-                  float cap) {
+                  float cap, const float* __restrict__ sinks) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -104,7 +105,8 @@ attn_split_kernel(T* out, const T* q, long long q_stride, const T* kcache, const
     __syncwarp();
     const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
 
-    float m = -INFINITY, l = 0.f;
+    // a sink: one more term exp(sinks[h]) in the denominator, with no key and no value
+    float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f;
     float acc[MAX_D / 32];
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; i++) acc[i] = 0.f;
@@ -169,7 +171,7 @@ int launch_rope(T* qkv, long long stride, const float* cos_t, const float* sin_t
 template <typename T>
 int launch_attn(T* out, const T* q, long long q_stride, const T* kcache, const T* vcache, const int* tables,
                 int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H, int G, int dk, int dv,
-                int window, float scale, float cap, cudaStream_t st) {
+                int window, float scale, float cap, const float* sinks, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (dk < 1 || dk > MAX_D || dv < 1 || dv > MAX_D || G < 1 || H % G) return OE_ERR_UNSUPPORTED;
     const long long items = (long long)n_tokens * H;
@@ -177,7 +179,7 @@ int launch_attn(T* out, const T* q, long long q_stride, const T* kcache, const T
     if (blocks > 2147483647LL) return OE_ERR_UNSUPPORTED;
     return oe_launch(attn_split_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), WARPS * dk * sizeof(float), st, out, q,
                      q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk, dv, window, scale,
-                     cap);
+                     cap, sinks);
 }
 
 }  // namespace
@@ -199,14 +201,14 @@ int oe_rope_split_kv_write_bf16(bf16* qkv, long long stride, const float* cos_t,
 }
 int oe_attn_split_f32(float* out, const float* q, long long q_stride, const float* kcache, const float* vcache,
                       const int* tables, int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H,
-                      int G, int dk, int dv, int window, float scale, float cap, cudaStream_t st) {
+                      int G, int dk, int dv, int window, float scale, float cap, const float* sinks, cudaStream_t st) {
     return launch_attn<float>(out, q, q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk,
-                              dv, window, scale, cap, st);
+                              dv, window, scale, cap, sinks, st);
 }
 int oe_attn_split_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* kcache, const bf16* vcache,
                        const int* tables, int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H,
-                       int G, int dk, int dv, int window, float scale, float cap, cudaStream_t st) {
+                       int G, int dk, int dv, int window, float scale, float cap, const float* sinks, cudaStream_t st) {
     return launch_attn<bf16>(out, q, q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk,
-                             dv, window, scale, cap, st);
+                             dv, window, scale, cap, sinks, st);
 }
 }

@@ -57,6 +57,7 @@ struct Args {
     int tokens_per_tile;
     int n_splits;              // > 1: every sequence brings one token; grid x is the split
     float* partial;            // [T, H, n_splits, DV + 2] when n_splits > 1
+    const float* sinks;        // null, or [H] float32: exp(sinks[h]) joins the softmax's denominator (no key, no value)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -267,6 +268,21 @@ attn_split_mma_kernel(const Args a) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
+    if (a.sinks && a.n_splits <= 1) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (!valid[i]) continue;
+            const float sk = a.sinks[head[i]] * LOG2E;
+            if (m_run[i] == -INFINITY) l_run[i] = 1.f;
+            else if (sk <= m_run[i]) l_run[i] += exp2f(sk - m_run[i]);
+            else {                                        // the sink is the largest term: rescale to it
+                const float f = exp2f(m_run[i] - sk);
+                l_run[i] = l_run[i] * f + 1.f;
+#pragma unroll
+                for (int n = 0; n < DV / 8; n++) { oacc[n][2 * i] *= f; oacc[n][2 * i + 1] *= f; }
+            }
+        }
+    }
     if (a.n_splits > 1) {
 #pragma unroll
         for (int i = 0; i < 2; i++) {
@@ -294,7 +310,8 @@ attn_split_mma_kernel(const Args a) {
 
 // One block per (token, head): the splits' sums put together in split order.  Maxima are in units of log2(e).
 __global__ void __launch_bounds__(128)
-attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int* __restrict__ seq_qlen, int H) {
+attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int* __restrict__ seq_qlen, int H,
+                        const float* __restrict__ sinks) {
     pdl_launch_dependents();
     pdl_wait();
     if (seq_qlen[blockIdx.x / H] <= 0) {                 // a padding sequence: nothing was written for it
@@ -302,9 +319,11 @@ attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int
         return;
     }
     const float* p = partial + (size_t)blockIdx.x * n_splits * (DV + 2);
-    float m = -INFINITY;
+    // a sink counts as one more split: maximum sinks[h] (in units of log2(e)), denominator 1, no values
+    const float sk = sinks ? sinks[blockIdx.x % H] * 1.4426950408889634f : -INFINITY;
+    float m = sk;
     for (int s = 0; s < n_splits; s++) m = fmaxf(m, p[(size_t)s * (DV + 2) + DV]);
-    float l = 0.f;
+    float l = sinks ? exp2f(sk - m) : 0.f;
     for (int s = 0; s < n_splits; s++) {
         const float ms = p[(size_t)s * (DV + 2) + DV];
         if (ms != -INFINITY) l += exp2f(ms - m) * p[(size_t)s * (DV + 2) + DV + 1];
@@ -330,7 +349,7 @@ int oe_attn_split_mma_dims(int* dk, int* dv) { *dk = DK; *dv = DV; return 0; }
 int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* kcache, const bf16* vcache,
                       const int* tables, int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen,
                       int n_seqs, int max_qlen, int H, int KVH, int window, float scale, float cap, int n_splits,
-                      float* partial, cudaStream_t st) {
+                      float* partial, const float* sinks, cudaStream_t st) {
     if (n_seqs <= 0 || max_qlen <= 0) return 0;
     if (KVH < 1 || H % KVH || H / KVH > NWARPS * 16 || n_seqs > 65535 || KVH > 65535) return OE_ERR_UNSUPPORTED;
     if (n_splits > 1 && (max_qlen != 1 || partial == nullptr)) return OE_ERR_UNSUPPORTED;
@@ -341,6 +360,7 @@ int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* 
     a.tokens_per_tile = (NWARPS * 16) / (H / KVH);
     a.n_splits = n_splits > 1 ? n_splits : 1;
     a.partial = partial;
+    a.sinks = sinks;
     const size_t smem = (size_t)2 * (K_TILE + V_TILE);
     static bool attr_set = false;
     if (!attr_set) {
@@ -352,7 +372,7 @@ int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* 
         // every sequence brings one token: row b of out is sequence b's (padding sequences leave theirs alone)
         const int rc = oe_launch(attn_split_mma_kernel, dim3(a.n_splits, KVH, n_seqs), dim3(NWARPS * 32), smem, st, a);
         if (rc) return rc;
-        return oe_launch(attn_split_merge_kernel, dim3(n_seqs * H), dim3(128), 0, st, out, (const float*)partial, a.n_splits, seq_qlen, H);
+        return oe_launch(attn_split_merge_kernel, dim3(n_seqs * H), dim3(128), 0, st, out, (const float*)partial, a.n_splits, seq_qlen, H, sinks);
     }
     const dim3 grid((max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile, KVH, n_seqs);
     return oe_launch(attn_split_mma_kernel, grid, dim3(NWARPS * 32), smem, st, a);

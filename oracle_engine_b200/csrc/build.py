@@ -42,6 +42,9 @@ LIBRARIES = {
     "stream": ("stream.cu", []),
     "gla": ("gla.cu", []),
     "attention_latent": ("attention_latent.cu", []),
+    "tokenwise": ("tokenwise.cu", []),
+    "attention_prep": ("attention_prep.cu", []),
+    "general_delta": ("general_delta.cu", []),
     "gemm_tc": ("gemm_tcgen05.cu", []),
     "gemm_pair": ("gemm_tcgen05_pair.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),

@@ -7,7 +7,8 @@
 //                   dense [T, E + (has_gate != 0)]: an expert's weight where it was chosen, zero elsewhere, and
 //                   in the last column sigmoid(gate logit) (has_gate 1) or one (has_gate 2: a shared expert without
 //                   a gate; z then holds no column for it).  mode 1: the weight of a chosen expert is the sigmoid
-//                   of its own logit, not renormalised (the choice is by the same order).
+//                   of its own logit, not renormalised (the choice is by the same order).  With `bias` (one float32
+//                   per expert, mode 1 only) the choice is by sigmoid(z) + bias and the weight stays sigmoid(z).
 //   moe_dense_act   gu [T, 2 F] holds, for F = E ff + shared_ff columns, the gate rows and, F columns further, the
 //                   up rows of all experts (expert e owns columns e ff .. (e + 1) ff - 1, the shared expert the last
 //                   shared_ff).  a[t, c] = silu(gate) * up * dense[t, expert of c]: the experts a token did not
@@ -19,7 +20,7 @@ namespace {
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, int mode, int* idx, float* wt, float* dense,
-                 const int* __restrict__ tok_seq, int n_tokens) {
+                 const int* __restrict__ tok_seq, int n_tokens, const float* __restrict__ bias) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -45,7 +46,7 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
         int bi = 0x7fffffff;
         for (int i = 0, e = lane; e < E; e += 32, i++) {
             if (taken >> i & 1u) continue;
-            const float v = zr[e];
+            const float v = bias ? 1.f / (1.f + expf(-zr[e])) + bias[e] : zr[e];
             if (v > best || (v == best && e < bi)) { best = v; bi = e; }
         }
 #pragma unroll
@@ -57,7 +58,7 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
         if (bi == 0x7fffffff) break;         // fewer experts than `top`
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (j == 0) zmax = best;
-        const float p = mode == 1 ? 1.f / (1.f + expf(-best)) : expf(best - zmax);
+        const float p = mode == 1 ? 1.f / (1.f + expf(-(bias ? zr[bi] : best))) : expf(best - zmax);
         sum += p;
         if (lane == 0) {
             if (idx) idx[(size_t)t * top + j] = bi;
@@ -78,7 +79,8 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
 // their gate and up values being read.
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
-moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, int scale_input) {
+moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, int scale_input,
+                     int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     const int per_row = F / V;
@@ -101,7 +103,11 @@ moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F,
             }
 #pragma unroll
             for (int i = 0; i < V; i++) {
-                if (scale_input) {
+                if (act == 1) {
+                    const float gf = fminf(to_f32(g[i]), limit);
+                    const float uf = fminf(fmaxf(to_f32(u[i]), -limit), limit);
+                    out[i] = from_f32<T>(gf / (1.f + expf(-1.702f * gf)) * (uf + 1.f) * w);
+                } else if (scale_input) {
                     const float gf = to_f32(g[i]) * w;
                     out[i] = from_f32<T>(gf / (1.f + expf(-gf)) * (to_f32(u[i]) * w));
                 } else {
@@ -120,17 +126,17 @@ moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F,
 
 template <typename T>
 int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, int scale_input,
-               cudaStream_t st) {
+               int act, float limit, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (F < 1 || ff < 1 || E < 0) return OE_ERR_UNSUPPORTED;
+    if (F < 1 || ff < 1 || E < 0 || act < 0 || act > 1 || (act == 1 && scale_input)) return OE_ERR_UNSUPPORTED;
     // 16-byte pieces: bfloat16, every expert's columns and the row a multiple of 8, aligned pointers
     const bool vec = sizeof(T) == 2 && ff % 8 == 0 && F % 8 == 0 && !(((uintptr_t)a | (uintptr_t)gu) & 15);
     const size_t total = (size_t)n_tokens * (vec ? F / 8 : F);
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vec)
-        return oe_launch(moe_dense_act_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input);
-    return oe_launch(moe_dense_act_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input);
+        return oe_launch(moe_dense_act_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input, act, limit);
+    return oe_launch(moe_dense_act_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W, scale_input, act, limit);
 }
 
 }  // namespace
@@ -138,19 +144,19 @@ int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E
 extern "C" {
 
 int oe_moe_route(const float* z, long long ldz, int E, int top, int has_gate, int mode, int* idx, float* wt, float* dense,
-                 const int* tok_seq, int n_tokens, cudaStream_t st) {
+                 const int* tok_seq, int n_tokens, const float* bias, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (E < 1 || E > 1024 || top < 1) return OE_ERR_UNSUPPORTED;
+    if (E < 1 || E > 1024 || top < 1 || (bias != nullptr && mode != 1)) return OE_ERR_UNSUPPORTED;
     return oe_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, st, z, ldz, E, top, has_gate, mode, idx, wt, dense,
-                     tok_seq, n_tokens);
+                     tok_seq, n_tokens, bias);
 }
 int oe_moe_dense_act_f32(float* a, const float* gu, const float* dense, int n_tokens, int F, int E, int ff, int W,
-                         int scale_input, cudaStream_t st) {
-    return launch_act<float>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, st);
+                         int scale_input, int act, float limit, cudaStream_t st) {
+    return launch_act<float>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, act, limit, st);
 }
 int oe_moe_dense_act_bf16(bf16* a, const bf16* gu, const float* dense, int n_tokens, int F, int E, int ff, int W,
-                          int scale_input, cudaStream_t st) {
-    return launch_act<bf16>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, st);
+                          int scale_input, int act, float limit, cudaStream_t st) {
+    return launch_act<bf16>(a, gu, dense, n_tokens, F, E, ff, W, scale_input, act, limit, st);
 }
 
 }  // extern "C"

@@ -56,15 +56,32 @@ _SIGNATURES = {
     },
     "attention_split": {
         "oe_rope_split_kv_write": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "oe_attn_split": [_P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+        "oe_attn_split": [_P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
+    },
+    "attention_prep": {
+        "oe_qkv_norm_rot_write": [_P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _P, _I, _P, _P,
+                                  _I, _I, _I, _I, _I, _P],
+        "oe_unrotate_heads": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    },
+    "tokenwise": {
+        "oe_dyt_norm": [_P, _P, _P, _P, _F, _L, _I, _P],
+        "oe_pair_embed": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _F, _P, _P],
+        "oe_prev_token_update": [_P, _P, _P, _P, _I, _P],
+        "oe_pass_entry_add": [_P, _P, _P, _L, _I, _P],
+        "oe_scale_rows": [_P, _L, _F, _P],
+    },
+    "general_delta": {
+        "oe_gdelta_padded_dk": [_I],
+        "oe_gdelta_prepare": [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _I, _I, _P],
+        "oe_gdelta_scan": [_P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _P],
     },
     "retention": {
         "oe_retention_scan": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "oe_retention_chunks": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P],
     },
     "moe": {
-        "oe_moe_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P],
-        "oe_moe_dense_act": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "oe_moe_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P, _P],
+        "oe_moe_dense_act": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     },
     "stream": {
         "oe_group_rmsnorm": [_P, _P, _L, _P, _I, _I, _I, _F, _P],
@@ -99,7 +116,8 @@ _SIGNATURES = {
 _TYPED = {"oe_embed_gather", "oe_rmsnorm", "oe_rope_kv_write", "oe_swiglu", "oe_gemm_simple", "oe_attn_paged",
           "oe_relu2", "oe_tanh_rows", "oe_rot_norm_kv_write", "oe_token_shift_mix", "oe_last_rows_to_state",
           "oe_rope_split_kv_write", "oe_attn_split", "oe_moe_dense_act", "oe_group_rmsnorm", "oe_poly_norm",
-          "oe_side_gate", "oe_latent_write", "oe_attn_latent", "oe_head_matmul"}
+          "oe_side_gate", "oe_latent_write", "oe_attn_latent", "oe_head_matmul", "oe_dyt_norm", "oe_pair_embed",
+          "oe_qkv_norm_rot_write", "oe_unrotate_heads"}
 _fn_cache: dict[str, object] = {}
 
 
@@ -431,10 +449,15 @@ def rope_split_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.
 
 def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, tables: torch.Tensor,
                tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int, n_kv_heads: int, dk: int, dv: int,
-               window: int, scale: float, cap: float = 0.0) -> None:
+               window: int, scale: float, cap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
     """out[t] = softmax attention of token t's query heads over the keys (pos - window, pos] of its sequence, with
-    s <- cap tanh(s / cap) when cap > 0.  q [T, >= H dk] (row stride free), out contiguous [T, H dv]."""
-    _dev(out, q, kcache, vcache, tables, tok_seq, tok_pos)
+    s <- cap tanh(s / cap) when cap > 0.  q [T, >= H dk] (row stride free), out contiguous [T, H dv].  sinks (float32
+    [H] or None): exp(sinks[h]) is one more term of head h's denominator, without key or value."""
+    _dev(out, q, kcache, vcache, tables, tok_seq, tok_pos, sinks)
+    if sinks is not None:
+        _f32c(sinks, "sinks")
+        if sinks.numel() != n_heads:
+            raise KernelError("attn_split: sinks must hold one value per query head")
     for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
         _i32(t, n)
     if out.shape[1] != n_heads * dv or not out.is_contiguous() or q.stride(1) != 1 or q.dtype != out.dtype \
@@ -445,7 +468,195 @@ def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache:
     _check(_fn("attention_split", "oe_attn_split", out.dtype)(
         _ptr(out), _ptr(q), q.stride(0), _ptr(kcache), _ptr(vcache), _ptr(tables), tables.shape[1], _ptr(tok_seq),
         _ptr(tok_pos), out.shape[0], n_heads, n_kv_heads, dk, dv, int(window), float(scale), float(cap or 0.0),
-        _stream()), "attn_split")
+        _ptr(sinks), _stream()), "attn_split")
+
+
+# ---------------------------------------------------------------------------------------- attention_prep.cu
+
+def qkv_norm_rot_write(q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, proj: torch.Tensor,
+                       biases, norm_weights, eps: float, key_tables, rot_dims: int, value_tables, value_norm: bool,
+                       tables: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int,
+                       n_kv_heads: int, dk: int, dv: int) -> None:
+    """From the float32 projection rows proj [T, >= H dk + G dk + G dv] = [q | k | v]: adds `biases` (three float32
+    vectors or None), divides every q and k head by its root mean square and multiplies by `norm_weights` (two
+    float32 vectors [dk], or None: no norm), turns their first rot_dims dimensions by the position (halves paired;
+    key_tables = (cos, sin) float32 [positions, rot_dims/2] or None), divides every v head by its root mean square
+    when value_norm, and turns all dv dimensions of v by the position (value_tables = (cos, sin) [positions, dv/2] or
+    None).  q goes to q_out [T, H dk] (contiguous, the cache's dtype), k and v to the token's rows of the cache."""
+    qb, kb, vb = biases if biases is not None else (None, None, None)
+    qw, kw = norm_weights if norm_weights is not None else (None, None)
+    ck, sk = key_tables if key_tables is not None and rot_dims else (None, None)
+    cv, sv = value_tables if value_tables is not None else (None, None)
+    _dev(q_out, kcache, vcache, proj, qb, kb, vb, qw, kw, ck, sk, cv, sv, tables, tok_seq, tok_pos)
+    for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
+        _i32(t, n)
+    T = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < n_heads * dk + n_kv_heads * (dk + dv):
+        raise KernelError("qkv_norm_rot_write: proj must be float32 rows of at least H dk + G (dk + dv) values")
+    if tuple(q_out.shape) != (T, n_heads * dk) or not q_out.is_contiguous() or q_out.dtype not in _SUFFIX:
+        raise KernelError("qkv_norm_rot_write: q_out must be contiguous [T, H dk]")
+    if not _split_cache_ok(kcache, vcache, q_out.dtype, n_kv_heads, dk, dv):
+        raise KernelError("qkv_norm_rot_write: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv] of q_out's dtype")
+    for t, n, size in ((qb, "q bias", n_heads * dk), (kb, "k bias", n_kv_heads * dk), (vb, "v bias", n_kv_heads * dv),
+                       (qw, "q norm weight", dk), (kw, "k norm weight", dk)):
+        if t is not None:
+            _f32c(t, n)
+            if t.numel() != size:
+                raise KernelError(f"qkv_norm_rot_write: {n} must hold {size} values")
+    if (qw is None) != (kw is None):
+        raise KernelError("qkv_norm_rot_write: q and k are normed together or not at all")
+    if ck is not None:
+        _f32c(ck, "cos")
+        _f32c(sk, "sin")
+        if rot_dims % 2 or rot_dims > dk or ck.shape[1] != rot_dims // 2 or sk.shape != ck.shape:
+            raise KernelError("qkv_norm_rot_write: key tables must be [positions, rot_dims/2], rot_dims even and <= dk")
+    if cv is not None:
+        _f32c(cv, "value cos")
+        _f32c(sv, "value sin")
+        if dv % 2 or cv.shape[1] != dv // 2 or sv.shape != cv.shape:
+            raise KernelError("qkv_norm_rot_write: value tables must be [positions, dv/2], dv even")
+    _check(_fn("attention_prep", "oe_qkv_norm_rot_write", q_out.dtype)(
+        _ptr(q_out), _ptr(kcache), _ptr(vcache), _ptr(proj), proj.stride(0), _ptr(qb), _ptr(kb), _ptr(vb), _ptr(qw),
+        _ptr(kw), float(eps), _ptr(ck), _ptr(sk), int(rot_dims if ck is not None else 0), _ptr(cv), _ptr(sv),
+        int(bool(value_norm)), _ptr(tables), tables.shape[1], _ptr(tok_seq), _ptr(tok_pos), T, n_heads, n_kv_heads, dk, dv,
+        _stream()), "qkv_norm_rot_write")
+
+
+def unrotate_heads(o: torch.Tensor, value_tables, tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int,
+                   dv: int) -> None:
+    """Every head of o [T, H dv] (contiguous) turned back by its token's position, in place: the pair (m, m + dv/2)
+    by minus the angle whose cosine and sine value_tables = (cos, sin) float32 [positions, dv/2] hold."""
+    cv, sv = value_tables
+    _dev(o, cv, sv, tok_seq, tok_pos)
+    _i32(tok_seq, "tok_seq")
+    _i32(tok_pos, "tok_pos")
+    _f32c(cv, "value cos")
+    _f32c(sv, "value sin")
+    if o.dtype not in _SUFFIX or not o.is_contiguous() or o.shape[1] != n_heads * dv or dv % 2 \
+            or cv.shape[1] != dv // 2 or sv.shape != cv.shape:
+        raise KernelError("unrotate_heads: o contiguous [T, H dv], dv even, tables [positions, dv/2]")
+    _check(_fn("attention_prep", "oe_unrotate_heads", o.dtype)(
+        _ptr(o), _ptr(cv), _ptr(sv), _ptr(tok_seq), _ptr(tok_pos), o.shape[0], n_heads, dv, _stream()), "unrotate_heads")
+
+
+# ---------------------------------------------------------------------------------------- tokenwise.cu
+
+def dyt_norm(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: float) -> None:
+    """y = tanh(alpha x) * w + b; x float32 [rows, D], w and b float32 [D], y float32 or bfloat16 of x's shape."""
+    _dev(y, x, w, b)
+    for t, n in ((x, "x"), (w, "w"), (b, "b")):
+        _f32c(t, n)
+    D = x.shape[-1]
+    if y.shape != x.shape or not y.is_contiguous() or y.dtype not in _SUFFIX or w.numel() != D or b.numel() != D:
+        raise KernelError("dyt_norm: y contiguous of x's shape, w and b one value per column")
+    _check(_fn("tokenwise", "oe_dyt_norm", y.dtype)(_ptr(y), _ptr(x), _ptr(w), _ptr(b), float(alpha), x.numel() // D, D,
+                                                    _stream()), "dyt_norm")
+
+
+def pair_embed(x: torch.Tensor, table: torch.Tensor, pair: torch.Tensor | None, ctx, prev: torch.Tensor | None,
+               buckets: int, mul_prev: int, mul_cur: int, scale: float, err: torch.Tensor | None) -> None:
+    """x[t] = table[id_t] * scale + pair[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] as float32, row `buckets` of
+    `pair` for a sequence's first token; the token before a step's first one comes from prev [slots] int32.  pair
+    None: the scaled table row alone.  Padding rows get zeros; an id outside the table sets err[0] = 1."""
+    _dev(x, table, pair, prev, err, ctx.token_ids)
+    n, D = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or not table.is_contiguous() or table.shape[1] != D:
+        raise KernelError("pair_embed: x must be float32 [n, D] and table [V, D], contiguous")
+    if pair is not None:
+        if pair.dtype != table.dtype or not pair.is_contiguous() or tuple(pair.shape) != (buckets + 1, D):
+            raise KernelError("pair_embed: the pair table must be [buckets + 1, D] of the table's dtype")
+        if prev is None or prev.dtype != torch.int32 or not prev.is_contiguous():
+            raise KernelError("pair_embed: prev must be a contiguous int32 tensor, one value per slot")
+    if ctx.token_ids.numel() < n or ctx.tok_seq.numel() < n:
+        raise KernelError("pair_embed: fewer ids than rows")
+    _check(_fn("tokenwise", "oe_pair_embed", table.dtype)(
+        _ptr(x), _ptr(table), _ptr(pair), _ptr(ctx.token_ids), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.cu_q),
+        _ptr(ctx.seq_slot), _ptr(prev), n, D, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), float(scale),
+        _ptr(err), _stream()), "pair_embed")
+
+
+def prev_token_update(prev: torch.Tensor, ctx) -> None:
+    """prev[slot of sequence b] = the last token sequence b brings in this step."""
+    _dev(prev, ctx.token_ids)
+    if prev.dtype != torch.int32 or not prev.is_contiguous():
+        raise KernelError("prev_token_update: prev must be a contiguous int32 tensor")
+    _check(_fn("tokenwise", "oe_prev_token_update")(_ptr(prev), _ptr(ctx.token_ids), _ptr(ctx.cu_q), _ptr(ctx.seq_slot),
+                                                    ctx.n_seqs, _stream()), "prev_token_update")
+
+
+def pass_entry_add(x: torch.Tensor, e: torch.Tensor | None, s: torch.Tensor) -> None:
+    """x += e + s; x and e float32 [rows, D] (e may be None), s float32 [D]."""
+    _dev(x, e, s)
+    _f32c(x, "x")
+    _f32c(s, "s")
+    if e is not None:
+        _f32c(e, "e")
+        if e.shape != x.shape:
+            raise KernelError("pass_entry_add: e must have x's shape")
+    if s.numel() != x.shape[-1]:
+        raise KernelError("pass_entry_add: s must hold one value per column")
+    D = x.shape[-1]
+    _check(_fn("tokenwise", "oe_pass_entry_add")(_ptr(x), _ptr(e), _ptr(s), x.numel() // D, D, _stream()), "pass_entry_add")
+
+
+def scale_rows(x: torch.Tensor, s: float) -> None:
+    """x *= s; x float32, contiguous."""
+    _dev(x)
+    _f32c(x, "x")
+    _check(_fn("tokenwise", "oe_scale_rows")(_ptr(x), x.numel(), float(s), _stream()), "scale_rows")
+
+
+# ---------------------------------------------------------------------------------------- general_delta.cu
+
+def gdelta_padded_dk(dk: int) -> int:
+    """The number of key channels a packed row of gdelta_prepare holds per vector (dk rounded up), or -1."""
+    return int(_fn("general_delta", "oe_gdelta_padded_dk")(int(dk)))
+
+
+def gdelta_prepare(packed: torch.Tensor, proj: torch.Tensor, off_r: int, off_k: int, off_a: int, off_z1: int, rank: int,
+                   w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor | None, decay_coef: float, tok_seq: torch.Tensor,
+                   heads: int, dk: int) -> None:
+    """The vectors a generalized delta rule reads, from float32 projection rows: per (token, head)
+    [w | u | a u | k | r w] (each padded to gdelta_padded_dk(dk) values), c1 = sum r a u, c2 = r . k, with
+    w = exp(-decay_coef sigmoid(w2 tanh(z1) + w0)), a = sigmoid(za + a_bias), u = k / sqrt(|k|^2 + 1e-6)."""
+    _dev(packed, proj, w2, w0, a_bias, tok_seq)
+    _i32(tok_seq, "tok_seq")
+    for t, n in ((packed, "packed"), (w2, "w2"), (w0, "w0")):
+        _f32c(t, n)
+    T = proj.shape[0]
+    dkp = gdelta_padded_dk(dk)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelError("gdelta_prepare: proj must be float32 rows")
+    if dkp < 0 or tuple(packed.shape) != (T, heads, 5 * dkp + 4) or tuple(w2.shape) != (heads * dk, rank) \
+            or w0.numel() != heads * dk or (a_bias is not None and a_bias.numel() != heads * dk):
+        raise KernelError("gdelta_prepare: shapes do not agree")
+    for off, n in ((off_r, heads * dk), (off_k, heads * dk), (off_a, heads * dk), (off_z1, rank)):
+        if off < 0 or off + n > proj.shape[1]:
+            raise KernelError("gdelta_prepare: a column range lies outside the projection row")
+    if a_bias is not None:
+        _f32c(a_bias, "a_bias")
+    _check(_fn("general_delta", "oe_gdelta_prepare")(
+        _ptr(packed), _ptr(proj), proj.stride(0), off_r, off_k, off_a, off_z1, rank, _ptr(w2), _ptr(w0), _ptr(a_bias),
+        float(decay_coef), _ptr(tok_seq), T, heads, dk, _stream()), "gdelta_prepare")
+
+
+def gdelta_scan(o: torch.Tensor, state: torch.Tensor, packed: torch.Tensor, v: torch.Tensor, ctx, heads: int, dk: int,
+                dv: int) -> None:
+    """S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r for every token of the step, in order, per sequence and head.
+    o float32 [T, H dv] contiguous; state float32 [slots, H, dk, dv]; packed as gdelta_prepare left it; v float32
+    [T, H dv] (a view of the projection rows; row stride free)."""
+    _dev(o, state, packed, v)
+    for t, n in ((o, "o"), (state, "state"), (packed, "packed")):
+        _f32c(t, n)
+    T = o.shape[0]
+    dkp = gdelta_padded_dk(dk)
+    if dkp < 0 or tuple(o.shape) != (T, heads * dv) or tuple(state.shape[1:]) != (heads, dk, dv) \
+            or tuple(packed.shape) != (T, heads, 5 * dkp + 4) or v.dtype != torch.float32 or v.stride(1) != 1 \
+            or tuple(v.shape) != (T, heads * dv):
+        raise KernelError("gdelta_scan: shapes do not agree")
+    _check(_fn("general_delta", "oe_gdelta_scan")(
+        _ptr(o), _ptr(state), _ptr(packed), _ptr(v), v.stride(0), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), ctx.n_seqs, heads, dk,
+        dv, _stream()), "gdelta_scan")
 
 
 # ---------------------------------------------------------------------------------------- retention.cu
@@ -501,13 +712,19 @@ def retention_scratch(n_tokens: int, n_seqs: int, heads: int, dk: int, dv: int) 
 # ---------------------------------------------------------------------------------------- moe.cu
 
 def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate, dense: torch.Tensor, tok_seq: torch.Tensor,
-              idx: torch.Tensor | None = None, wt: torch.Tensor | None = None, weights: str = "softmax") -> None:
+              idx: torch.Tensor | None = None, wt: torch.Tensor | None = None, weights: str = "softmax",
+              bias: torch.Tensor | None = None) -> None:
     """From router logits z float32 [T, >= E (+ 1)]: dense [T, E (+ 1)] float32 gets each chosen expert's weight
     (zero elsewhere) and, with has_gate, sigmoid of column E in its last column (has_gate "one": the constant 1, a
     shared expert without a gate; z needs no column for it); idx int32 [T, top] and wt float32 [T, top] receive the
     choice itself when given.  weights "softmax": the softmax over the `top` largest logits alone; "sigmoid": each
-    chosen expert's own sigmoid(logit), not renormalised."""
-    _dev(z, dense, tok_seq, idx, wt)
+    chosen expert's own sigmoid(logit), not renormalised.  bias (float32 [E], with "sigmoid" only): the choice is by
+    sigmoid(logit) + bias, the weights stay the sigmoids."""
+    _dev(z, dense, tok_seq, idx, wt, bias)
+    if bias is not None:
+        _f32c(bias, "bias")
+        if weights != "sigmoid" or bias.numel() != n_experts:
+            raise KernelError("moe_route: a choice bias needs sigmoid weights and one value per expert")
     _i32(tok_seq, "tok_seq")
     _f32c(dense, "dense")
     T = z.shape[0]
@@ -528,15 +745,18 @@ def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate, dense: torch.
         if t is not None and tuple(t.shape) != (T, top):
             raise KernelError("moe_route: idx and wt must be [T, top]")
     _check(_fn("moe", "oe_moe_route")(_ptr(z), z.stride(0), n_experts, top, gate, int(weights == "sigmoid"), _ptr(idx), _ptr(wt),
-                                      _ptr(dense), _ptr(tok_seq), T, _stream()), "moe_route")
+                                      _ptr(dense), _ptr(tok_seq), T, _ptr(bias), _stream()), "moe_route")
 
 
 def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int,
-                  scale_input: bool = False) -> None:
+                  scale_input: bool = False, act: str = "silu", limit: float = 0.0) -> None:
     """a[t, c] = silu(gu[t, c]) * gu[t, F + c] * dense[t, group of c]; the group of column c is c // ff for the
     first n_experts * ff columns and the last column of dense for the rest (the shared expert).  scale_input: the
-    weight w = dense[t, group] multiplies the expert's input instead, a = silu(w gu[t, c]) * (w gu[t, F + c])."""
+    weight w = dense[t, group] multiplies the expert's input instead, a = silu(w gu[t, c]) * (w gu[t, F + c]).
+    act "clamped": with g = min(gate, limit) and u = clamp(up, -limit, limit), a = g * sigmoid(1.702 g) * (u + 1) * w."""
     _dev(a, gu, dense)
+    if act not in ("silu", "clamped") or (act == "clamped" and (scale_input or not limit > 0)):
+        raise KernelError("moe_dense_act: act is silu or clamped (with a positive limit, weight on the output)")
     _f32c(dense, "dense")
     T, F = a.shape
     if tuple(gu.shape) != (T, 2 * F) or gu.dtype != a.dtype or not (gu.is_contiguous() and a.is_contiguous()) \
@@ -544,7 +764,8 @@ def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_expe
             or (F > n_experts * ff and dense.shape[1] != n_experts + 1):
         raise KernelError("moe_dense_act: shapes do not agree")
     _check(_fn("moe", "oe_moe_dense_act", a.dtype)(_ptr(a), _ptr(gu), _ptr(dense), T, F, n_experts, ff, dense.shape[1],
-                                                   int(bool(scale_input)), _stream()), "moe_dense_act")
+                                                   int(bool(scale_input)), int(act == "clamped"), float(limit),
+                                                   _stream()), "moe_dense_act")
 
 
 # ---------------------------------------------------------------------------------------- stream.cu

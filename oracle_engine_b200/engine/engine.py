@@ -54,6 +54,9 @@ class Engine:
         for e, needs in enumerate(self.model.state_needs()):
             for name, need in needs.items():
                 self.state.add(e, name, need)
+        for name, need in self.model.embedding_state_needs().items():      # e.g. the token before a step's first one
+            self.state.add("embedding", name, need)
+        self.model.bind_embedding_state(self.state.views("embedding"))
         self.sampler = Sampler(self.state, self.device)
         self.stepper = Stepper(self.model, self.cache, self.state, self.rt, use_graphs)
         self._row_slot = torch.empty(self.cache.n_slots, dtype=torch.int32, device=self.device)

@@ -1,2 +1,2 @@
 """Architectures: importing this package registers each one under its config.json name."""
-from . import fovirax, fuvipel, llama, pusunex  # noqa: F401
+from . import bogupel, fovirax, fuvipel, llama, pusunex  # noqa: F401

@@ -53,12 +53,18 @@ def split_mixer_core(rt, out, qkv, cos, sin, rot, kcache, vcache, tables, ctx, H
     """Rotation, cache write and attention of an attention mixer whose keys and values have head sizes of their
     own and lie in two cache tensors, with a cap on the scores (parts/capped_attention.py)."""
     ops.rope_split_kv_write(qkv, cos, sin, rot, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, True)
+    split_attend(rt, out, qkv, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap)
+
+
+def split_attend(rt, out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks=None) -> None:
+    """Attention of queries that are turned already over keys and values that lie in two cache tensors; `sinks`
+    (float32 [H] or None): a learned score per head that joins the softmax's denominator without key or value."""
     if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.attention_split_supported(dk, dv, H, G):
-            ops_tc.attention_split(out, qkv, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap)
+            ops_tc.attention_split(out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks)
             return
-    ops.attn_split(out, qkv, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap)
+    ops.attn_split(out, q, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap, sinks)
 
 
 def latent_core(rt, out, qfull, rows, tables, ctx, H, r, rd, scale) -> None:

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
+from .registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, STREAM_PARTS
 from .spec import ModelSpec, TensorDecl
 
 # importing the modules registers the built-in parts
@@ -17,6 +17,7 @@ from . import attention, block, embedding, feedforward, norms, positions  # noqa
 from . import delta_rule, parallel, sink_attention, time_mix  # noqa: F401,E402
 from . import capped_attention, moe, retention  # noqa: F401,E402
 from . import gla, latent_attention  # noqa: F401,E402
+from . import general_delta, passes, rotated_value_attention  # noqa: F401,E402
 
 
 class DecoderModel:
@@ -31,6 +32,10 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, "", runtime)
         self.layers = [self._build_layer(ls) for ls in spec.layers]
         self.schedule = list(spec.schedule)
+        self.stream_parts = {name: STREAM_PARTS.get(ps.kind)(ps.params, "", runtime)
+                             for name, ps in spec.stream_parts.items()}
+        self._keep_embedding = any(getattr(p, "needs_embedding_output", False) for p in self.stream_parts.values())
+        self.embedding_state = {}          # the embedding's per-slot state tensors, bound by the engine
 
     def _build_layer(self, ls):
         mparams = dict(ls.mixer.params)
@@ -49,7 +54,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
-        parts = [self.embedding, self.final_norm, self.head]
+        parts = [self.embedding, self.final_norm, self.head] + list(self.stream_parts.values())
         for layer in self.layers:
             parts.extend(layer.parts())
         return parts
@@ -90,6 +95,13 @@ class DecoderModel:
         """Per schedule entry: dict name -> StateNeed of its mixer."""
         return [dict(self.layers[e.layer].mixer.state_need()) for e in self.schedule]
 
+    def embedding_state_needs(self):
+        """dict name -> StateNeed of what the embedding keeps per sequence (the token before, say)."""
+        return dict(self.embedding.state_need())
+
+    def bind_embedding_state(self, views: dict) -> None:
+        self.embedding_state = dict(views)
+
     # ------------------------------------------------------------------ what a step costs
     def step_bytes(self, contexts) -> int:
         """Bytes a step has to read from memory: every weight it uses once, and for each of its
@@ -124,7 +136,14 @@ class DecoderModel:
     # captured in a CUDA graph, so that one part that must run eagerly (a mixer that reads its state
     # on the host, say) does not take the graphs away from every other layer.
     def embed(self, ctx, out=None):
-        return self.embedding.forward(ctx.token_ids, ctx.n_tokens, out)
+        step = getattr(self.embedding, "forward_step", None)
+        x = step(ctx, self.embedding_state, out) if step is not None else \
+            self.embedding.forward(ctx.token_ids, ctx.n_tokens, out)
+        if self._keep_embedding:          # parts between the layers read the embedding's output of this pass
+            kept = self.rt.buffer("embedding_output", *x.shape, dtype=torch.float32)
+            kept.copy_(x)
+            self.rt.pass_store["embedding_output"] = kept
+        return x
 
     def run_entries(self, x, ctx, cache_views, state_views, lo: int, hi: int) -> None:
         if lo == 0:
@@ -136,6 +155,8 @@ class DecoderModel:
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             first = getattr(nxt, "first_weights", None)
             self.rt.next_weights = first() if first is not None else None
+            if e.before is not None:
+                self.stream_parts[e.before[0]].forward(x, ctx, **dict(e.before[1]))
             self.layers[e.layer].forward(x, ctx, cache_views[owner], state_views[i], e.cache_from is None)
         self.rt.next_weights = None
 
@@ -150,7 +171,8 @@ class DecoderModel:
         """[(graph_safe, first stage, one past the last stage)]: maximal runs of stages that are all
         safe to capture in a CUDA graph, or all not."""
         ok = lambda parts: all(getattr(p, "graph_safe", False) for p in parts)          # noqa: E731
-        flags = [ok([self.embedding])] + [ok(self.layers[e.layer].parts()) for e in self.schedule] + \
+        hook = lambda e: [] if e.before is None else [self.stream_parts[e.before[0]]]   # noqa: E731
+        flags = [ok([self.embedding])] + [ok(self.layers[e.layer].parts() + hook(e)) for e in self.schedule] + \
                 [ok([self.final_norm, self.head])]
         runs, lo = [], 0
         for i in range(1, len(flags) + 1):

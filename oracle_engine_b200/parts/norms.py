@@ -3,7 +3,9 @@ computed in float32 and stored in the compute dtype (reference: core/ops.cpp:149
 epsilon is a parameter here, always passed).  `add_into(dst, y, coef)` is the same norm applied to a
 sublayer's float32 OUTPUT and added, times coef, into another float32 tensor (layers that norm what
 a sublayer returns instead of what it reads).  With `groups` > 1 the row is cut into that many equal consecutive parts
-and each part is divided by its own root mean square (the weight still spans the whole row)."""
+and each part is divided by its own root mean square (the weight still spans the whole row).
+`dynamic_tanh`: y = tanh(alpha x) * w + b with one scalar alpha and the vectors w, b: a norm that computes no
+mean and no variance, so every value of a row is normed by itself."""
 from __future__ import annotations
 
 from ..csrc import ops
@@ -60,3 +62,36 @@ class RMSNorm(Part):
             ops.group_rmsnorm_add(dst, y, self.weight, self.eps, self.groups, coef, accumulate, cast)
         else:
             ops.rmsnorm_add(dst, y, self.weight, self.eps, coef, accumulate, cast)
+
+
+@NORMS.register("dynamic_tanh")
+class DynamicTanh(Part):
+    graph_safe = True
+    """params: size, name (the weight's tensor name under the prefix), bias and alpha (tensor names; default: the weight's
+    name + ".b" and + ".alpha").  alpha is a scalar tensor, read once when the weights are loaded."""
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.size = int(self._need("size"))
+        base = self._need("name")
+        self.name = prefix + base
+        self.bias_name = prefix + (self.params.get("bias") or base + ".b")
+        self.alpha_name = prefix + (self.params.get("alpha") or base + ".alpha")
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensors(self):
+        return [TensorDecl(self.name, (self.size,), "ones_normal"), TensorDecl(self.bias_name, (self.size,)),
+                TensorDecl(self.alpha_name, (), "ones_normal")]
+
+    def load(self, get):
+        self.weight, self.bias = self.rt.to_f32(get(self.name)), self.rt.to_f32(get(self.bias_name))
+        self.alpha = float(get(self.alpha_name).to("cpu", dtype=__import__("torch").float32).reshape(-1)[0])
+
+    def weight_bytes(self):
+        return 0 if self.weight is None else 2 * self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x):
+        y = self.rt.empty(*x.shape)
+        ops.dyt_norm(y, x, self.weight, self.bias, self.alpha)
+        return y

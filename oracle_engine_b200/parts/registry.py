@@ -39,6 +39,15 @@ Norm  (NORMS)
 PositionEncoding  (POSITIONS)            built once per model and name, shared by mixers
     tables(max_positions)                whatever its mixers read (e.g. cos/sin tables)
 
+Embedding  (EMBEDDINGS)
+    forward(ids, n_tokens, out)          the float32 stream of the step's tokens; one that keeps per-sequence state
+                                         declares it with state_need() and has forward_step(ctx, state, out) instead
+StreamPart  (STREAM_PARTS)               something a model does to the stream between layers (ModelSpec.stream_parts,
+                                         named by a ScheduleEntry's `before`)
+    forward(x, ctx, **arguments)         x float32 [T, hidden], updated in place; `needs_embedding_output = True` makes
+                                         the model keep the embedding's output of the pass in
+                                         runtime.pass_store["embedding_output"]
+
 Block  (BLOCKS)                          the arrangement of mixer, feed-forward and norms
     forward(x, ctx, cache, state, owns_cache)   x float32 [T, hidden], updated in place
     built as cls(mixer, feed_forward, mixer_norm, ffn_norm), or, when its LayerSpec gives `block_params`
@@ -85,6 +94,7 @@ NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
+STREAM_PARTS = Registry("stream part")
 HEADS = Registry("output head")
 
 

@@ -10,7 +10,8 @@ which model it is in: every part gets its sizes and constants from its `PartSpec
 * `ModelSpec.schedule` is the order in which layers run: a list of `ScheduleEntry`.  An
   entry may name a layer that another entry also names (the weights are shared; each entry
   still has a cache of its own), and `cache_from` lets an entry read the cache that an
-  earlier entry wrote instead of writing one (it then computes no keys or values).
+  earlier entry wrote instead of writing one (it then computes no keys or values), and `before` names a part
+  of `ModelSpec.stream_parts` that works on the stream right before the entry's layer.
 
 The reference has one fixed arrangement, x += Attn(RMSNorm(x)); x += FFN(RMSNorm(x)),
 L times (core/model.cpp:361-474); here that order is the data a Llama spec holds.
@@ -51,6 +52,9 @@ class LayerSpec:
 class ScheduleEntry:
     layer: int                         # index into ModelSpec.layers
     cache_from: Optional[int] = None   # index of an earlier schedule entry whose cache is read
+    # (name in ModelSpec.stream_parts, ((argument, value), ...)): a part that works on the stream right before this
+    # entry's layer, e.g. what a looped group of layers adds when a pass begins
+    before: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -107,11 +111,14 @@ class ModelSpec:
     stop_ids: tuple = ()
     bos_id: Optional[int] = None
     ignored_tensors: tuple = ()        # name suffixes a file may hold that the model does not read
+    stream_parts: dict = field(default_factory=dict)   # name -> PartSpec of a part that schedule entries run `before` their layer
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {e.layer}, there are {len(self.layers)}")
+            if e.before is not None and e.before[0] not in self.stream_parts:
+                raise ValueError(f"schedule[{i}].before names the stream part {e.before[0]!r}, which the model does not have")
             if e.cache_from is not None:
                 if not 0 <= e.cache_from < i:
                     raise ValueError(f"schedule[{i}].cache_from must name an earlier entry, got {e.cache_from}")
