@@ -6,7 +6,7 @@
     python bench.py --shape 8b --workload baseline      # 32 prompts of 128..4,096 tokens, 256 steps
     python bench.py --profile [--batch 64]              # device time per kind of kernel, on standard error
     python bench.py --impl reference --steps K          # the reference's own benchmark program (CPU)
-    python bench.py --design fuvipel|fovirax|pusunex [--beside llama,fovirax] [--widths 1024,2048,3072] [--profile]
+    python bench.py --design fuvipel|fovirax|pusunex|bogupel [--beside llama,fovirax] [--widths 1024,2048,3072] [--profile]
                                                         # that design beside a Llama of equal width and depth
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default
@@ -419,6 +419,27 @@ def pusunex_shape(width: int, layers: int, vocab: int) -> dict:
             "token_side": {"dim": 64}, "layers": out}
 
 
+def bogupel_shape(width: int, layers: int, vocab: int) -> dict:
+    """A Bogupel of real layer sizes: two attention layers, then a generalized-delta layer, repeated.  Attention with
+    heads of 128 for keys and values (four query heads to a key head, a window of 1,024 keys, half of each key head
+    turned, frequencies rescaled by wavelength, values turned over all 128 dimensions); delta layers with width / 64
+    heads of 64 (states of 64 x 64) and a decay projection of rank 64; on every layer a mixture of 8 clamped experts of
+    2/3 x width, two chosen (Fovirax's routed experts without its shared one); a pair table of 65,521 buckets.  No
+    loop: as many distinct layers as runs."""
+    heads = width // 128
+    ff = (2 * width // 3 + 63) // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                     "mask": {"size": 1024},
+                     "rot": {"dims": 64, "base": 500000.0,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    delta = {"type": "general_delta", "mlp": moe, "mixer": {"heads": width // 64, "dim": 64, "rank": 64}}
+    return {"architecture": "Bogupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [delta if i % 3 == 2 else att for i in range(layers)]}
+
+
 def llama_shape(width: int, layers: int, vocab: int) -> dict:
     """The Llama decoder of the same width, depth and vocabulary: heads of 128, four query heads to a key head,
     a SwiGLU of 8/3 x width (the same weights as a two-matrix feed-forward of 4 x width)."""
@@ -434,6 +455,7 @@ def design_compare(args) -> int:
     time per kind of kernel instead."""
     import torch
     from oracle_engine_b200 import LlamaConfig
+    from oracle_engine_b200.config.bogupel import BogupelConfig
     from oracle_engine_b200.config.fovirax import FoviraxConfig
     from oracle_engine_b200.config.fuvipel import FuvipelConfig
     from oracle_engine_b200.config.pusunex import PusunexConfig
@@ -441,6 +463,7 @@ def design_compare(args) -> int:
     designs = {"fuvipel": lambda *a: FuvipelConfig.from_dict(fuvipel_shape(*a)),
                "fovirax": lambda *a: FoviraxConfig.from_dict(fovirax_shape(*a)),
                "pusunex": lambda *a: PusunexConfig.from_dict(pusunex_shape(*a)),
+               "bogupel": lambda *a: BogupelConfig.from_dict(bogupel_shape(*a)),
                "llama": lambda *a: LlamaConfig.from_dict(llama_shape(*a))}
     beside = [b for b in (args.beside or "llama").split(",") if b and b != args.design]
     unknown = [b for b in beside if b not in designs]
@@ -600,7 +623,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
-    ap.add_argument("--design", default=None, choices=["fuvipel", "fovirax", "pusunex"],
+    ap.add_argument("--design", default=None, choices=["fuvipel", "fovirax", "pusunex", "bogupel"],
                     help="measure this design beside the Llama decoder at equal sizes instead of the headline workload")
     ap.add_argument("--beside", default=None, help="the designs to measure beside --design, comma-separated (default llama)")
     ap.add_argument("--widths", default="1024,2048,3072", help="model widths of --design")

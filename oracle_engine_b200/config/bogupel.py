@@ -11,7 +11,8 @@ config.json of this design:
     layers          a list; each entry has `type` ("attention" or "general_delta"), `mixer` and `mlp` (an object or null)
       mixer of "attention"       heads, kv_heads, dim, vdim, scale; optional mask {size}, rot {dims, base, optional
                                  scaling {factor, low, high, original}}
-      mixer of "general_delta"   heads, dim
+      mixer of "general_delta"   heads, dim; optional rank (of the decay's two-matrix projection: the weight file
+                                 gives it, the key is for writing folders of random weights)
       mlp           kind "moe", expert {ff, limit}, router {experts, top}
 Every key below the top level is checked and an unknown one is refused: it would be a mechanism this code does not
 have.  Top-level keys beyond these are a file's own notes.  The design has no largest position, no stop tokens and
@@ -68,9 +69,12 @@ def _attention(raw, what) -> dict:
 
 def _general_delta(raw, what) -> dict:
     raw = _obj(raw, what)
-    _only(raw, what, ("heads", "dim"))
+    _only(raw, what, ("heads", "dim", "rank"))
     r = _Reader(raw)
-    return {"heads": r.integer("heads"), "dim": r.integer("dim")}
+    m = {"heads": r.integer("heads"), "dim": r.integer("dim")}
+    if raw.get("rank") is not None:          # the file's tensors give it; the key lets folders of random weights be written
+        m["rank"] = r.integer("rank")
+    return m
 
 
 def _moe(raw, what) -> dict:

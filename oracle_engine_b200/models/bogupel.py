@@ -57,7 +57,7 @@ def build_spec(cfg: BogupelConfig, max_positions: int | None = None) -> ModelSpe
                 "value_position": None if rot is None else position(m["vdim"], rot["base"], None)})
         else:
             mixer = PartSpec("general_delta", {"hidden_size": D, "num_heads": m["heads"], "head_dim": m["dim"],
-                                               "eps": eps})
+                                               "eps": eps, "rank": m.get("rank")})
         mlp = layer["mlp"]
         ffn = None if mlp is None else PartSpec("moe_swiglu", {
             "hidden_size": D, "num_experts": mlp["router"]["experts"], "top": mlp["router"]["top"],

@@ -160,11 +160,16 @@ def general_delta(h, w, pre, m, eps):
     return y @ w[pre + "o"].T
 
 
-def moe(h, w, pre, mlp):
+def moe(h, w, pre, mlp, gaps=None):
+    """gaps (a list or None) receives, per token, how far the last chosen expert's choice score lies above the best
+    one that was not chosen."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     lim = float(mlp["expert"]["limit"])
     s = torch.sigmoid(h @ w[pre + "router"].T)
     chosen = torch.topk(s + w[pre + "correction"], top, dim=-1).indices
+    if gaps is not None and top < E:
+        ranked = torch.sort(s + w[pre + "correction"], dim=-1, descending=True).values
+        gaps.append(ranked[:, top - 1] - ranked[:, top])
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -187,7 +192,7 @@ def layer_order(cfg):
     return out + [(i, None, False) for i in range(b, n)]
 
 
-def forward(cfg, w, tokens, keep_layers=False):
+def forward(cfg, w, tokens, keep_layers=False, gaps=None):
     """Logits [T, vocab] of one sequence from its first token (and the stream after every layer run)."""
     eps = cfg["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -209,7 +214,7 @@ def forward(cfg, w, tokens, keep_layers=False):
             raise ValueError(L["type"])
         if L.get("mlp"):
             n2 = dyt(x, w[pre + "norm2.alpha"], w[pre + "norm2"], w[pre + "norm2.b"])
-            x = x + moe(n2, w, pre + "mlp.", L["mlp"])
+            x = x + moe(n2, w, pre + "mlp.", L["mlp"], gaps)
         kept.append(x.clone())
     xn = dyt(x, w["final.norm.alpha"], w["final.norm"], w["final.norm.b"])
     logits = xn @ w["head"].T * float(cfg.get("logit_scale", 1.0))
@@ -219,3 +224,32 @@ def forward(cfg, w, tokens, keep_layers=False):
 def load(folder):
     folder = Path(folder)
     return json.loads((folder / "config.json").read_text()), read_safetensors(folder / "model.safetensors")
+
+
+class PlainBogupel:
+    def __init__(self, folder):
+        self.cfg, self.w = load(folder)
+
+    def logits(self, tokens):
+        return forward(self.cfg, self.w, tokens)
+
+    def layers(self, tokens):
+        """The stream after every layer run (a looped layer counts each time), [runs, T, D]."""
+        return forward(self.cfg, self.w, tokens, keep_layers=True)[1]
+
+    def close_calls(self, tokens, margin):
+        """The positions at which some router's choice hangs on less than `margin` of a score: arithmetic of fewer
+        bits may choose otherwise there, and no comparison at reduced precision should rest on them."""
+        gaps = []
+        forward(self.cfg, self.w, tokens, gaps=gaps)
+        if not gaps:
+            return set()
+        return set(torch.nonzero(torch.stack(gaps).min(0).values < margin).flatten().tolist())
+
+
+def generate(plain, prompt, n_new):
+    """Greedy continuation, the whole sequence recomputed for every token."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain.logits(toks)[-1].argmax()))
+    return toks[len(prompt):]
