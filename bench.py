@@ -486,14 +486,18 @@ def design_compare(args) -> int:
                 del engine
                 torch.cuda.empty_cache()
                 continue
+            note = lambda what: print(f"[bench] {name} width {width}: {what}", file=sys.stderr, flush=True)    # noqa: E731
+            note(f"built; prompt of {PREFILL_TOKENS} tokens")
             ms, fl = time_prefill(engine, [PREFILL_TOKENS], vocab, runs=5, warmup=3, settle_ms=args.settle_ms)
             out = {"prefill_tok_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
                    "prefill_frac_of_bf16_peak": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                    "weights_gb": round(engine.model.step_bytes([]) / 1e9, 3)}
+            note(f"{ms:.3f} ms; 8 prompts of {PROMPT_LEN} tokens")
             ms8, _ = time_prefill(engine, [PROMPT_LEN] * 8, vocab, runs=5, warmup=3, settle_ms=args.settle_ms)
             out["prefill_8x%d_tok_s" % PROMPT_LEN] = round(8 * PROMPT_LEN / (ms8 / 1e3), 1)
             out["prefill_8x%d_ms" % PROMPT_LEN] = round(ms8, 3)
             for b in (8, 64):
+                note(f"decoding {b} sequences")
                 d = time_decode(engine, [PROMPT_LEN] * b, min(args.steps, 64), args.warmup, vocab, 3, args.settle_ms)
                 out[f"decode_b{b}_tok_s"] = round(d["tok_s"], 1)
                 out[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)

@@ -13,6 +13,8 @@
 //                         32-bit path's attention, and the bfloat16 path's for head sizes that the tensor-core
 //                         kernel (attention_split_mma.cu) does not take.  `sinks` (null, or one float32 per query
 //                         head): the softmax's denominator also holds exp(sinks[h]), a term without key or value.
+//                         `unrot_cos`, `unrot_sin` (null, or float32 [positions, dv/2]): every head's result is turned
+//                         back by its query's position, pair (m, m + dv/2), before it is stored.
 #include "common.cuh"
 
 namespace {
@@ -81,7 +83,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_split_kernel(T* out, const T* q, long long q_stride, const T* kcache, const T* vcache,
                   const int* __restrict__ tables, int max_pages, const int* __restrict__ tok_seq,
                   const int* __restrict__ tok_pos, int n_tokens, int H, int G, int dk, int dv, int window, float scale,
-                  float cap, const float* __restrict__ sinks) {
+                  float cap, const float* __restrict__ sinks, const float* __restrict__ unrot_cos,
+                  const float* __restrict__ unrot_sin) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -89,7 +92,7 @@ attn_split_kernel(T* out, const T* q, long long q_stride, const T* kcache, const
     const long long item = (long long)blockIdx.x * WARPS + warp;
     if (item >= (long long)n_tokens * H) return;
     const int t = (int)(item / H), h = (int)(item % H);
-    float* qs = qs_all + warp * dk;
+    float* qs = qs_all + warp * max(dk, dv);
     T* o = out + (size_t)t * H * dv + (size_t)h * dv;
     const int b = tok_seq[t];
     if (b < 0) {
@@ -146,6 +149,26 @@ attn_split_kernel(T* out, const T* q, long long q_stride, const T* kcache, const
         m = m_new;
     }
     const float inv = 1.f / l;
+    if (unrot_cos != nullptr) {
+        // the result turned back by the query's position: pair (m, m + dv/2) by minus the table's angle
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; i++) {
+            const int d = lane + 32 * i;
+            if (d < dv) qs[d] = acc[i] * inv;
+        }
+        __syncwarp();
+        const int half = dv / 2;
+        const float* cr = unrot_cos + (size_t)pos * half;
+        const float* sr = unrot_sin + (size_t)pos * half;
+        for (int d = lane; d < dv; d += 32) {
+            float r = qs[d];
+            if (d < half) r = qs[d] * cr[d] + qs[d + half] * sr[d];
+            else if (d < 2 * half) r = qs[d] * cr[d - half] - qs[d - half] * sr[d - half];
+            o[d] = from_f32<T>(r);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; i++) {
         const int d = lane + 32 * i;
@@ -171,15 +194,17 @@ int launch_rope(T* qkv, long long stride, const float* cos_t, const float* sin_t
 template <typename T>
 int launch_attn(T* out, const T* q, long long q_stride, const T* kcache, const T* vcache, const int* tables,
                 int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H, int G, int dk, int dv,
-                int window, float scale, float cap, const float* sinks, cudaStream_t st) {
+                int window, float scale, float cap, const float* sinks, const float* unrot_cos, const float* unrot_sin,
+                cudaStream_t st) {
     if (n_tokens <= 0) return 0;
+    if (unrot_cos == nullptr || unrot_sin == nullptr) unrot_cos = unrot_sin = nullptr;
     if (dk < 1 || dk > MAX_D || dv < 1 || dv > MAX_D || G < 1 || H % G) return OE_ERR_UNSUPPORTED;
     const long long items = (long long)n_tokens * H;
     const long long blocks = (items + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return OE_ERR_UNSUPPORTED;
-    return oe_launch(attn_split_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), WARPS * dk * sizeof(float), st, out, q,
+    return oe_launch(attn_split_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), WARPS * (dk > dv ? dk : dv) * sizeof(float), st, out, q,
                      q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk, dv, window, scale,
-                     cap, sinks);
+                     cap, sinks, unrot_cos, unrot_sin);
 }
 
 }  // namespace
@@ -201,14 +226,16 @@ int oe_rope_split_kv_write_bf16(bf16* qkv, long long stride, const float* cos_t,
 }
 int oe_attn_split_f32(float* out, const float* q, long long q_stride, const float* kcache, const float* vcache,
                       const int* tables, int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H,
-                      int G, int dk, int dv, int window, float scale, float cap, const float* sinks, cudaStream_t st) {
+                      int G, int dk, int dv, int window, float scale, float cap, const float* sinks,
+                      const float* unrot_cos, const float* unrot_sin, cudaStream_t st) {
     return launch_attn<float>(out, q, q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk,
-                              dv, window, scale, cap, sinks, st);
+                              dv, window, scale, cap, sinks, unrot_cos, unrot_sin, st);
 }
 int oe_attn_split_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* kcache, const bf16* vcache,
                        const int* tables, int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H,
-                       int G, int dk, int dv, int window, float scale, float cap, const float* sinks, cudaStream_t st) {
+                       int G, int dk, int dv, int window, float scale, float cap, const float* sinks,
+                       const float* unrot_cos, const float* unrot_sin, cudaStream_t st) {
     return launch_attn<bf16>(out, q, q_stride, kcache, vcache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, G, dk,
-                             dv, window, scale, cap, sinks, st);
+                             dv, window, scale, cap, sinks, unrot_cos, unrot_sin, st);
 }
 }

@@ -58,6 +58,8 @@ struct Args {
     int n_splits;              // > 1: every sequence brings one token; grid x is the split
     float* partial;            // [T, H, n_splits, DV + 2] when n_splits > 1
     const float* sinks;        // null, or [H] float32: exp(sinks[h]) joins the softmax's denominator (no key, no value)
+    const float* unrot_cos;    // null, or [positions, DV/2] float32 (with unrot_sin): every head's result is turned back by
+    const float* unrot_sin;    //   its query's position, pair (m, m + DV/2) by minus the table's angle, before it is stored
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -302,6 +304,20 @@ attn_split_mma_kernel(const Args a) {
         if (!valid[i]) continue;
         const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
         bf16* o = a.out + (packed0 + tok[i]) * (long long)(a.H * DV) + (size_t)head[i] * DV + tig * 2;
+        if (a.unrot_cos != nullptr) {
+            // column m of the first half and m + DV/2 lie in the same thread: accumulators n and n + DV/16
+            const float* cr = a.unrot_cos + (size_t)pos[i] * (DV / 2) + tig * 2;
+            const float* sr = a.unrot_sin + (size_t)pos[i] * (DV / 2) + tig * 2;
+#pragma unroll
+            for (int n = 0; n < DV / 16; n++) {
+                const float2 c = *(const float2*)(cr + n * 8), s = *(const float2*)(sr + n * 8);
+                const float u0 = oacc[n][2 * i] * inv, u1 = oacc[n][2 * i + 1] * inv;
+                const float v0 = oacc[n + DV / 16][2 * i] * inv, v1 = oacc[n + DV / 16][2 * i + 1] * inv;
+                *(uint32_t*)(o + n * 8) = pack_bf16(u0 * c.x + v0 * s.x, u1 * c.y + v1 * s.y);
+                *(uint32_t*)(o + n * 8 + DV / 2) = pack_bf16(v0 * c.x - u0 * s.x, v1 * c.y - u1 * s.y);
+            }
+            continue;
+        }
 #pragma unroll
         for (int n = 0; n < DV / 8; n++)
             *(uint32_t*)(o + n * 8) = pack_bf16(oacc[n][2 * i] * inv, oacc[n][2 * i + 1] * inv);
@@ -311,7 +327,8 @@ attn_split_mma_kernel(const Args a) {
 // One block per (token, head): the splits' sums put together in split order.  Maxima are in units of log2(e).
 __global__ void __launch_bounds__(128)
 attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int* __restrict__ seq_qlen, int H,
-                        const float* __restrict__ sinks) {
+                        const float* __restrict__ sinks, const float* __restrict__ unrot_cos,
+                        const float* __restrict__ unrot_sin, const int* __restrict__ seq_start) {
     pdl_launch_dependents();
     pdl_wait();
     if (seq_qlen[blockIdx.x / H] <= 0) {                 // a padding sequence: nothing was written for it
@@ -329,6 +346,27 @@ attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int
         if (ms != -INFINITY) l += exp2f(ms - m) * p[(size_t)s * (DV + 2) + DV + 1];
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (unrot_cos != nullptr) {
+        // the sequence's one token stands at position seq_start; a thread takes a pair (d, d + DV/2) and turns it back
+        const size_t at = (size_t)seq_start[blockIdx.x / H] * (DV / 2);
+        for (int d = threadIdx.x; d < DV / 2; d += blockDim.x) {
+            float u = 0.f, v = 0.f;
+            for (int s = 0; s < n_splits; s++) {
+                const float ms = p[(size_t)s * (DV + 2) + DV];
+                if (ms != -INFINITY) {
+                    const float f = exp2f(ms - m);
+                    u = fmaf(f, p[(size_t)s * (DV + 2) + d], u);
+                    v = fmaf(f, p[(size_t)s * (DV + 2) + d + DV / 2], v);
+                }
+            }
+            u *= inv;
+            v *= inv;
+            const float c = unrot_cos[at + d], sn = unrot_sin[at + d];
+            out[(size_t)blockIdx.x * DV + d] = __float2bfloat16_rn(u * c + v * sn);
+            out[(size_t)blockIdx.x * DV + d + DV / 2] = __float2bfloat16_rn(v * c - u * sn);
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < DV; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; s++) {
@@ -349,7 +387,7 @@ int oe_attn_split_mma_dims(int* dk, int* dv) { *dk = DK; *dv = DV; return 0; }
 int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* kcache, const bf16* vcache,
                       const int* tables, int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen,
                       int n_seqs, int max_qlen, int H, int KVH, int window, float scale, float cap, int n_splits,
-                      float* partial, const float* sinks, cudaStream_t st) {
+                      float* partial, const float* sinks, const float* unrot_cos, const float* unrot_sin, cudaStream_t st) {
     if (n_seqs <= 0 || max_qlen <= 0) return 0;
     if (KVH < 1 || H % KVH || H / KVH > NWARPS * 16 || n_seqs > 65535 || KVH > 65535) return OE_ERR_UNSUPPORTED;
     if (n_splits > 1 && (max_qlen != 1 || partial == nullptr)) return OE_ERR_UNSUPPORTED;
@@ -361,6 +399,10 @@ int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* 
     a.n_splits = n_splits > 1 ? n_splits : 1;
     a.partial = partial;
     a.sinks = sinks;
+    const bool unrot = unrot_cos != nullptr && unrot_sin != nullptr;
+    // with several splits the merge turns the result back, not the kernel that writes the parts
+    a.unrot_cos = unrot && a.n_splits <= 1 ? unrot_cos : nullptr;
+    a.unrot_sin = unrot && a.n_splits <= 1 ? unrot_sin : nullptr;
     const size_t smem = (size_t)2 * (K_TILE + V_TILE);
     static bool attr_set = false;
     if (!attr_set) {
@@ -372,7 +414,8 @@ int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* 
         // every sequence brings one token: row b of out is sequence b's (padding sequences leave theirs alone)
         const int rc = oe_launch(attn_split_mma_kernel, dim3(a.n_splits, KVH, n_seqs), dim3(NWARPS * 32), smem, st, a);
         if (rc) return rc;
-        return oe_launch(attn_split_merge_kernel, dim3(n_seqs * H), dim3(128), 0, st, out, (const float*)partial, a.n_splits, seq_qlen, H, sinks);
+        return oe_launch(attn_split_merge_kernel, dim3(n_seqs * H), dim3(128), 0, st, out, (const float*)partial, a.n_splits, seq_qlen, H, sinks,
+                         unrot ? unrot_cos : (const float*)nullptr, unrot ? unrot_sin : (const float*)nullptr, seq_start);
     }
     const dim3 grid((max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile, KVH, n_seqs);
     return oe_launch(attn_split_mma_kernel, grid, dim3(NWARPS * 32), smem, st, a);

@@ -153,6 +153,21 @@ def build(name: str, verbose: bool = True, defines=None) -> Path:
     return out
 
 
+_early_launch = [True]
+
+
+def set_early_launch(on: bool) -> None:
+    """Whether kernels are launched with programmatic stream serialization (they may start while their predecessor
+    drains) from now on, in every library loaded now or later.  OE_PDL=0 in the environment switches it off for good."""
+    on = bool(on)
+    with _lock:
+        if _early_launch[0] == on:
+            return
+        _early_launch[0] = on
+        for lib in _loaded.values():
+            lib.oe_pdl_set(int(on))
+
+
 def load(name: str, defines=None) -> ctypes.CDLL:
     """The loaded library `name`, built first if needed."""
     key = name + _define_flags(defines)[0]
@@ -160,6 +175,10 @@ def load(name: str, defines=None) -> ctypes.CDLL:
         lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(str(build(name, defines=defines)))
+            lib.oe_pdl_set.argtypes = [ctypes.c_int]
+            lib.oe_pdl_set.restype = None
+            if not _early_launch[0]:
+                lib.oe_pdl_set(0)
             _loaded[key] = lib
         return lib
 

@@ -44,6 +44,14 @@ static inline int oe_pdl_enabled() {
 }
 #endif
 
+// The attribute can also be switched at run time, per library (every library is one translation unit and exports its
+// own oe_pdl_set): the step function launches large prompt steps without it (engine/step.py says why).
+#ifndef __CUDA_ARCH__
+static int oe_pdl_runtime_flag = 1;
+extern "C" __attribute__((visibility("default"))) void oe_pdl_set(int on) { oe_pdl_runtime_flag = on ? 1 : 0; }
+static inline int oe_pdl_now() { return oe_pdl_enabled() && oe_pdl_runtime_flag; }
+#endif
+
 template <typename... KArgs, typename... Args>
 static inline int oe_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                Args... args) {
@@ -55,7 +63,7 @@ static inline int oe_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
 #ifndef __CUDA_ARCH__
-    attr[0].val.programmaticStreamSerializationAllowed = early ? oe_pdl_enabled() : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = early ? oe_pdl_now() : 0;
 #endif
     cfg.attrs = attr;
     cfg.numAttrs = 1;
@@ -74,7 +82,7 @@ static inline int oe_launch_cluster(void (*kernel)(KArgs...), unsigned cluster_x
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
 #ifndef __CUDA_ARCH__
-    attr[0].val.programmaticStreamSerializationAllowed = oe_pdl_enabled();
+    attr[0].val.programmaticStreamSerializationAllowed = oe_pdl_now();
 #endif
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = cluster_x;

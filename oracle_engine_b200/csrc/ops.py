@@ -56,7 +56,7 @@ _SIGNATURES = {
     },
     "attention_split": {
         "oe_rope_split_kv_write": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "oe_attn_split": [_P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
+        "oe_attn_split": [_P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P, _P, _P],
     },
     "attention_prep": {
         "oe_qkv_norm_rot_write": [_P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _P, _I, _P, _P,
@@ -146,6 +146,13 @@ def _stream() -> int:
 
 
 LAUNCHES = [0]          # kernels launched through this module (or captured into a graph)
+# ORACLE_SYNC_LAUNCHES=1: the host waits for every kernel right after its launch and names, on standard error, the
+# ones that take longer than a second (with what they were launched for): the way to find a kernel that stands
+# still, since with the stream running ahead the host only ever waits in the step's last call.
+import os as _os
+import sys as _sys
+import time as _time
+SYNC_LAUNCHES = _os.environ.get("ORACLE_SYNC_LAUNCHES", "") not in ("", "0")
 OBSERVER = [None]       # engine/profile.py: an object whose mark(what, detail) hears of every launch
 
 
@@ -154,6 +161,12 @@ def _check(code: int, what: str, detail=None) -> None:
         LAUNCHES[0] += 1
         if OBSERVER[0] is not None:
             OBSERVER[0].mark(what, detail)
+        if SYNC_LAUNCHES and not torch.cuda.is_current_stream_capturing():
+            t0 = _time.time()
+            print(f"[launch] {what} {detail if detail is not None else ''}", file=_sys.stderr, flush=True)
+            torch.cuda.synchronize()
+            if _time.time() - t0 > 1.0:
+                print(f"[launch] {what} took {_time.time() - t0:.1f} s", file=_sys.stderr, flush=True)
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: sizes outside what this kernel takes")
@@ -447,13 +460,28 @@ def rope_split_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.
         _stream()), "rope_split_kv_write")
 
 
+def _unrotate_tables(unrotate, dv: int, what: str):
+    """(cos, sin) checked: float32 [positions, dv/2] on the device, dv even; (None, None) if there is nothing to turn."""
+    if unrotate is None:
+        return None, None
+    uc, us = unrotate
+    _dev(uc, us)
+    _f32c(uc, "cos")
+    _f32c(us, "sin")
+    if dv % 2 or uc.dim() != 2 or uc.shape[1] != dv // 2 or us.shape != uc.shape:
+        raise KernelError(f"{what}: the tables of the turn back must be [positions, dv/2], dv even")
+    return uc, us
+
+
 def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, tables: torch.Tensor,
                tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int, n_kv_heads: int, dk: int, dv: int,
-               window: int, scale: float, cap: float = 0.0, sinks: torch.Tensor | None = None) -> None:
+               window: int, scale: float, cap: float = 0.0, sinks: torch.Tensor | None = None, unrotate=None) -> None:
     """out[t] = softmax attention of token t's query heads over the keys (pos - window, pos] of its sequence, with
     s <- cap tanh(s / cap) when cap > 0.  q [T, >= H dk] (row stride free), out contiguous [T, H dv].  sinks (float32
-    [H] or None): exp(sinks[h]) is one more term of head h's denominator, without key or value."""
+    [H] or None): exp(sinks[h]) is one more term of head h's denominator, without key or value.  unrotate ((cos, sin)
+    float32 [positions, dv/2] or None): every head's result is turned back by its query's position before it is stored."""
     _dev(out, q, kcache, vcache, tables, tok_seq, tok_pos, sinks)
+    uc, us = _unrotate_tables(unrotate, dv, "attn_split")
     if sinks is not None:
         _f32c(sinks, "sinks")
         if sinks.numel() != n_heads:
@@ -468,7 +496,7 @@ def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache:
     _check(_fn("attention_split", "oe_attn_split", out.dtype)(
         _ptr(out), _ptr(q), q.stride(0), _ptr(kcache), _ptr(vcache), _ptr(tables), tables.shape[1], _ptr(tok_seq),
         _ptr(tok_pos), out.shape[0], n_heads, n_kv_heads, dk, dv, int(window), float(scale), float(cap or 0.0),
-        _ptr(sinks), _stream()), "attn_split")
+        _ptr(sinks), _ptr(uc), _ptr(us), _stream()), "attn_split")
 
 
 # ---------------------------------------------------------------------------------------- attention_prep.cu

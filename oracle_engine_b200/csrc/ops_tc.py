@@ -590,18 +590,22 @@ def _attn_split_lib(dk: int, dv: int, shared: bool = False):
         lib = _build.load("attention_split_tc", defines=defines)
         fn = lib.oe_attn_split_mma
         fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p]
+                       c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p]
         fn.restype = c_int
         _split_libs[(dk, dv, shared)] = fn
     return fn
 
 
 def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, window: int,
-                    scale: float, cap: float, sinks=None) -> None:
+                    scale: float, cap: float, sinks=None, unrotate=None) -> None:
     """out[t] = attention of token t's query heads over the keys (pos - window, pos] of its sequence, scores capped
     by cap tanh(s / cap) when cap > 0; bfloat16, q rotated already (rows of q may be a view of the fused product),
     kcache [pages, G, PAGE, dk], vcache [pages, G, PAGE, dv]; vcache None: the values are the first dv columns of the
-    key rows.  sinks (float32 [H] or None): exp(sinks[h]) joins head h's denominator, without key or value."""
+    key rows.  sinks (float32 [H] or None): exp(sinks[h]) joins head h's denominator, without key or value.  unrotate
+    ((cos, sin) float32 [positions, dv/2] or None): every head's result is turned back by its query's position, pair
+    (m, m + dv/2), before it is stored (by the merge kernel when the keys are split)."""
+    uc, us = ops._unrotate_tables(unrotate, dv, "attention_split")
     if sinks is not None and (sinks.dtype != torch.float32 or not sinks.is_contiguous() or sinks.numel() != n_heads):
         raise ops.KernelError("attention_split: sinks must be float32, one value per query head")
     from .ops import PAGE
@@ -632,7 +636,7 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
                                    ctx.seq_qlen.data_ptr(), ctx.n_seqs, int(ctx.max_qlen), n_heads, n_kv_heads, int(window),
                                    float(scale), float(cap or 0.0), n_splits,
                                    None if partial is None else partial.data_ptr(),
-                                   None if sinks is None else sinks.data_ptr(), ops._stream())
+                                   None if sinks is None else sinks.data_ptr(), ops._ptr(uc), ops._ptr(us), ops._stream())
     ops._check(code, "attention_split_mma")
     if n_splits > 1:
         ops.LAUNCHES[0] += 1

@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from ..cache.kv_cache import CacheView
+from ..csrc import build as _build
 from ..csrc import ops
 from .batch import SequenceStep, StepBuffers, build_plan, context_class
 
@@ -28,6 +29,7 @@ _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # tokens mixed) is captured as well, per padded token count, padded batch size and context class: launched
 # one by one its 230 kernels cost the host 3.1 ms, twice what the device needs for them.
 GRAPH_STEP_TOKENS = 256
+EARLY_LAUNCH_MAX_TOKENS = 512       # steps of more tokens launch their kernels without programmatic stream serialization
 MAX_TOKEN_GRAPHS = 64
 MAX_GRAPH_WANTED_ROWS = 64
 _TOKEN_BUCKETS = (16, 32, 64, 128, 256)
@@ -167,7 +169,19 @@ class Stepper:
         if device_tokens is not None:
             ctx.token_ids[:len(seqs)].copy_(device_tokens[:len(seqs)])
         self.last_h2d_bytes = buf.bytes()
-        return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+        # Large steps launch without programmatic stream serialization.  With it, a prompt step of 8 x 512 tokens at a
+        # width of 2,048 (mixtures of experts, two-SM products, thousands of CTAs per kernel) stood still on the device
+        # about once in ten to forty steps, for minutes, in three designs; without it 100 such steps in a row ran
+        # through.  What the early starts win is in the chains of short kernels of small steps (a third of a decode step),
+        # where nothing of the kind was ever seen; on a prompt step of thousands of tokens they win 3 %.
+        calm = plan.n_tokens > EARLY_LAUNCH_MAX_TOKENS
+        if calm:
+            _build.set_early_launch(False)
+        try:
+            return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+        finally:
+            if calm:
+                _build.set_early_launch(True)
 
     def _run_graph(self, g, ctx):
         """The forward pass of a step whose shapes are those of `g`: directly at the first use (loads the

@@ -56,15 +56,19 @@ def split_mixer_core(rt, out, qkv, cos, sin, rot, kcache, vcache, tables, ctx, H
     split_attend(rt, out, qkv, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap)
 
 
-def split_attend(rt, out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks=None) -> None:
+def split_attend(rt, out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks=None,
+                 unrotate=None) -> None:
     """Attention of queries that are turned already over keys and values that lie in two cache tensors; `sinks`
-    (float32 [H] or None): a learned score per head that joins the softmax's denominator without key or value."""
+    (float32 [H] or None): a learned score per head that joins the softmax's denominator without key or value;
+    `unrotate` ((cos, sin) tables [positions, dv/2] or None): every head's result is turned back by its query's
+    position inside the kernel that stores it."""
     if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.attention_split_supported(dk, dv, H, G):
-            ops_tc.attention_split(out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks)
+            ops_tc.attention_split(out, q, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap, sinks, unrotate)
             return
-    ops.attn_split(out, q, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap, sinks)
+    ops.attn_split(out, q, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap, sinks,
+                   unrotate)
 
 
 def latent_core(rt, out, qfull, rows, tables, ctx, H, r, rd, scale) -> None:

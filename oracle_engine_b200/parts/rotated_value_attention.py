@@ -130,7 +130,5 @@ class RotatedValueAttention(Part):
         o = self.rt.buffer("rva.o", T, self.H * self.dv)
         from . import attention_dispatch as ad
         ad.split_attend(self.rt, o, q, kc, vc, cache.tables, ctx, self.H, self.G, self.dk, self.dv, self.window, self.scale,
-                        0.0, self.sinks)
-        if value_tables is not None:
-            ops.unrotate_heads(o, value_tables, ctx.tok_seq, ctx.tok_pos, self.H, self.dv)
+                        0.0, self.sinks, unrotate=value_tables)      # the turn back happens where the result is stored
         matmul_nt(self.rt, residual, o, self.w_o, accumulate=not overwrite)

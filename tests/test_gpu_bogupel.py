@@ -294,9 +294,16 @@ def test_attention_kernels_alone_with_one_key_that_stands_out(dtype, dk, dv, ten
                                    (f32(w["q.norm"]), f32(w["k.norm"])), eps, key_tables, rotd, value_tables, True,
                                    tables.cuda(), ctx.tok_seq, ctx.tok_pos, H, G, dk, dv)
             out = torch.zeros(T, H * dv, dtype=tdt, device="cuda")
-            ad.split_attend(rt, out, qo, kc, vc, tables.cuda(), ctx, H, G, dk, dv, window, scale, 0.0, f32(w["sink"]))
-            ops.unrotate_heads(out, value_tables, ctx.tok_seq, ctx.tok_pos, H, dv)
+            ad.split_attend(rt, out, qo, kc, vc, tables.cuda(), ctx, H, G, dk, dv, window, scale, 0.0, f32(w["sink"]),
+                            unrotate=value_tables)               # the turn back inside the kernel that stores the result
             got[lo:hi] = out
+            if inside is None:                                    # ... and as a kernel of its own behind the attention
+                apart = torch.zeros(T, H * dv, dtype=tdt, device="cuda")
+                ad.split_attend(rt, apart, qo, kc, vc, tables.cuda(), ctx, H, G, dk, dv, window, scale, 0.0, f32(w["sink"]))
+                ops.unrotate_heads(apart, value_tables, ctx.tok_seq, ctx.tok_pos, H, dv)
+                d = (apart.double() - out.double()).abs().max().item()
+                # bfloat16: the kernel of its own turns a result that was rounded once already
+                assert d < (1e-6 if dtype == "float32" else 2e-2 * max(1.0, out.abs().max().item())), (dtype, dk, dv, lo, d)
         tol = 2e-5 if dtype == "float32" else 3e-2
         err = (got.double().cpu() - want).abs().max().item()
         assert err < tol * max(1.0, want.abs().max().item()), (dtype, dk, dv, inside, err)
