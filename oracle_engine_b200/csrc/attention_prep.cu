@@ -56,35 +56,40 @@ qkv_norm_rot_write_kernel(T* q_out, T* kcache, T* vcache, const PrepArgs a) {
     const float* bias = kind == 0 ? a.qb : (kind == 1 ? a.kb : a.vb);
     const float* w = kind == 0 ? a.qw : (kind == 1 ? a.kw : nullptr);
     const bool normed = kind == 2 ? a.v_norm != 0 : w != nullptr;
-    float v[MAX_D / 32];
+    // everything a lane loads is asked for before the sums: the row's values, the bias, the norm weight and the angles
+    const int rot = kind == 2 ? (a.cos_v ? a.dv : 0) : a.rot;
+    const int half = rot / 2;
+    const float* cr = (kind == 2 ? a.cos_v : a.cos_k) + (size_t)pos * half;
+    const float* sr = (kind == 2 ? a.sin_v : a.sin_k) + (size_t)pos * half;
+    const int page = kind == 0 ? 0 : a.tables[(size_t)b * a.max_pages + pos / OE_PAGE];
+    float v[MAX_D / 32], wn[MAX_D / 32], cs[MAX_D / 32], sn[MAX_D / 32];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < MAX_D / 32; j++) {
         const int i = lane + 32 * j;
-        v[j] = 0.f;
+        v[j] = 0.f; wn[j] = 1.f; cs[j] = 1.f; sn[j] = 0.f;
         if (i < d) {
             v[j] = src[i] + (bias ? bias[(kind == 2 ? (long long)head * a.dv : (long long)head * a.dk) + i] : 0.f);
-            ss = fmaf(v[j], v[j], ss);
+            if (w) wn[j] = w[i];
+            if (i < rot) { const int m = i < half ? i : i - half; cs[j] = cr[m]; sn[j] = sr[m]; }
         }
     }
+#pragma unroll
+    for (int j = 0; j < MAX_D / 32; j++) ss = fmaf(v[j], v[j], ss);
     ss = warp_sum(ss);
     const float s = normed ? 1.f / sqrtf(ss / (float)d + a.eps) : 1.f;
     float* sm = stage[warp];
 #pragma unroll
     for (int j = 0; j < MAX_D / 32; j++) {
         const int i = lane + 32 * j;
-        if (i < d) sm[i] = (v[j] * s) * (w ? w[i] : 1.f);
+        v[j] = (v[j] * s) * wn[j];
+        if (i < rot) sm[i] = v[j];               // only the turned dimensions need their partner
     }
     __syncwarp();
-    const int rot = kind == 2 ? (a.cos_v ? a.dv : 0) : a.rot;
-    const int half = rot / 2;
-    const float* cr = (kind == 2 ? a.cos_v : a.cos_k) + (size_t)pos * half;
-    const float* sr = (kind == 2 ? a.sin_v : a.sin_k) + (size_t)pos * half;
     T* dst;
     if (kind == 0) {
         dst = q_out + ((size_t)t * a.H + head) * a.dk;
     } else {
-        const int page = a.tables[(size_t)b * a.max_pages + pos / OE_PAGE];
         if (page < 0) return;
         dst = (kind == 1 ? kcache : vcache) + (((size_t)page * a.G + head) * OE_PAGE + (pos % OE_PAGE)) * d;
     }
@@ -92,9 +97,9 @@ qkv_norm_rot_write_kernel(T* q_out, T* kcache, T* vcache, const PrepArgs a) {
     for (int j = 0; j < MAX_D / 32; j++) {
         const int i = lane + 32 * j;
         if (i >= d) continue;
-        float r = sm[i];
-        if (i < half) r = sm[i] * cr[i] - sm[i + half] * sr[i];
-        else if (i < rot) r = sm[i] * cr[i - half] + sm[i - half] * sr[i - half];
+        float r = v[j];
+        if (i < half) r = v[j] * cs[j] - sm[i + half] * sn[j];
+        else if (i < rot) r = v[j] * cs[j] + sm[i - half] * sn[j];
         dst[i] = from_f32<T>(r);
     }
 }

@@ -5,7 +5,7 @@
 // (both terms read the old S), with a decay w and a removal rate a per key channel:
 //     w = exp(-c * sigmoid(W2 tanh(z1) + w0)),   a = sigmoid(za + ba).
 //
-//   gdelta_prepare   one block per (token, head): from the float32 projection row (columns of r, k, v, za and z1 at
+//   gdelta_prepare   one block per (tile of tokens, head): from the float32 projection row (columns of r, k, v, za and z1 at
 //                    given offsets) the vectors the scan reads, one packed row [w | u | a u | k | r w] with every
 //                    vector padded to DKP values by zeros, then c1 = sum r a u and c2 = r . k.  The small product
 //                    with W2 [H dk, rank] is done here, in float32.
@@ -35,59 +35,97 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
-// grid (tokens, heads), 128 threads.  packed [T, H, 5 DKP + TAIL].
-__global__ void __launch_bounds__(128)
+// grid (token tiles, heads), 4 warps.  packed [T, H, 5 DKP + TAIL].  A block takes `tile` consecutive tokens of one head,
+// a warp one token at a time (its lanes own the head's key channels, lane + 32 e; every sum is a warp's, so the tokens
+// of a block do not wait for one another).  With w2_smem the head's rows of W2 come into shared memory once per block
+// (transposed, so that the lanes read consecutive words) and serve all its tokens; for a handful of tokens they are
+// read where they lie.  Either way a channel's sum runs over the rank in the same order.
+constexpr int PREP_WARPS = 4;
+
+// PREP_E: channels a lane owns (1, 2, 4 or 8: head sizes up to 32, 64, 128, 256), a compile-time count so that the loop
+// over the rank carries no instruction for channels the head does not have
+template <int PREP_E>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
 gdelta_prepare_kernel(float* packed, const float* proj, long long ld, int off_r, int off_k, int off_a, int off_z1, int rank,
                       const float* __restrict__ w2, const float* __restrict__ w0, const float* __restrict__ a_bias,
-                      float decay_coef, const int* __restrict__ tok_seq, int H, int dk, int DKP) {
-    __shared__ float red[32];
-    extern __shared__ float z1s[];               // tanh of the token's low-rank decay input, [rank]
+                      float decay_coef, const int* __restrict__ tok_seq, int n_tokens, int H, int dk, int DKP, int tile,
+                      int w2_smem) {
+    extern __shared__ float dyn[];               // tanh(z1) of the tile's tokens [tile][rank], then W2^T of the head [rank][dk | 1]
     pdl_launch_dependents();
+    float* z1s = dyn;
+    float* w2s = dyn + (size_t)tile * rank;
+    const int ws = dk | 1;                       // an odd row length: the transposing stores hit different banks
+    const int h = blockIdx.y, t0 = blockIdx.x * tile;
+    const int nt = min(tile, n_tokens - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (w2_smem) {                               // weights: not written by any kernel, so they may come before the wait
+        const float* src = w2 + (size_t)h * dk * rank;
+        for (int e = threadIdx.x; e < dk * rank; e += blockDim.x) w2s[(size_t)(e % rank) * ws + e / rank] = src[e];
+    }
     pdl_wait();
-    const int t = blockIdx.x, h = blockIdx.y;
-    if (tok_seq[t] < 0) return;
-    const float* row = proj + (size_t)t * ld;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) z1s[j] = tanhf(row[off_z1 + j]);
-    float* out = packed + ((size_t)t * H + h) * (size_t)(5 * DKP + TAIL);
-    // up to 256 key channels: two a thread
-    float kk[2] = {0.f, 0.f}, rr[2] = {0.f, 0.f};
-    float ss = 0.f;
+    for (int e = threadIdx.x; e < nt * rank; e += blockDim.x)
+        z1s[e] = tanhf(proj[(size_t)(t0 + e / rank) * ld + off_z1 + e % rank]);
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += PREP_WARPS) {
+        const int t = t0 + tt;
+        if (tok_seq[t] < 0) continue;
+        const float* row = proj + (size_t)t * ld;
+        const float* z1 = z1s + (size_t)tt * rank;
+        float* out = packed + ((size_t)t * H + h) * (size_t)(5 * DKP + TAIL);
+        float kk[PREP_E], rr[PREP_E], za[PREP_E], z[PREP_E];
+        float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const int i = threadIdx.x + e * 128;
-        if (i < dk) {
-            kk[e] = row[off_k + h * dk + i];
-            rr[e] = row[off_r + h * dk + i];
-            ss = fmaf(kk[e], kk[e], ss);
-        }
-    }
-    ss = block_sum(ss, red);                     // also orders the writes of z1s before the reads below
-    const float inv = 1.f / sqrtf(ss + 1e-6f);
-    float c1 = 0.f, c2 = 0.f;
-#pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const int i = threadIdx.x + e * 128;
-        if (i < DKP) {
-            float w = 0.f, u = 0.f, au = 0.f, rw = 0.f;
+        for (int e = 0; e < PREP_E; e++) {
+            const int i = lane + 32 * e;
+            kk[e] = rr[e] = za[e] = z[e] = 0.f;
             if (i < dk) {
-                const int c = h * dk + i;
-                float z = w0[c];
-                const float* w2r = w2 + (size_t)c * rank;
-                for (int j = 0; j < rank; j++) z = fmaf(w2r[j], z1s[j], z);
-                w = expf(-decay_coef * sigmoid_f(z));
-                const float a = sigmoid_f(row[off_a + c] + (a_bias ? a_bias[c] : 0.f));
-                u = kk[e] * inv;
-                au = a * u;
-                rw = rr[e] * w;
-                c1 = fmaf(rr[e], au, c1);
-                c2 = fmaf(rr[e], kk[e], c2);
+                kk[e] = row[off_k + h * dk + i];
+                rr[e] = row[off_r + h * dk + i];
+                za[e] = row[off_a + h * dk + i] + (a_bias ? a_bias[h * dk + i] : 0.f);
+                z[e] = w0[h * dk + i];
             }
-            out[i] = w; out[DKP + i] = u; out[2 * DKP + i] = au; out[3 * DKP + i] = kk[e]; out[4 * DKP + i] = rw;
         }
+#pragma unroll
+        for (int e = 0; e < PREP_E; e++) ss = fmaf(kk[e], kk[e], ss);
+        if (w2_smem) {
+            for (int j = 0; j < rank; j++) {
+                const float zj = z1[j];
+#pragma unroll
+                for (int e = 0; e < PREP_E; e++)
+                    if (lane + 32 * e < dk) z[e] = fmaf(w2s[(size_t)j * ws + lane + 32 * e], zj, z[e]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < PREP_E; e++) {
+                if (lane + 32 * e < dk) {
+                    const float* w2r = w2 + (size_t)(h * dk + lane + 32 * e) * rank;
+                    for (int j = 0; j < rank; j++) z[e] = fmaf(w2r[j], z1[j], z[e]);
+                }
+            }
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss + 1e-6f);
+        float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int e = 0; e < PREP_E; e++) {
+            const int i = lane + 32 * e;
+            if (i < DKP) {
+                float w = 0.f, u = 0.f, au = 0.f, rw = 0.f;
+                if (i < dk) {
+                    w = expf(-decay_coef * sigmoid_f(z[e]));
+                    u = kk[e] * inv;
+                    au = sigmoid_f(za[e]) * u;
+                    rw = rr[e] * w;
+                    c1 = fmaf(rr[e], au, c1);
+                    c2 = fmaf(rr[e], kk[e], c2);
+                }
+                out[i] = w; out[DKP + i] = u; out[2 * DKP + i] = au; out[3 * DKP + i] = kk[e]; out[4 * DKP + i] = rw;
+            }
+        }
+        c1 = warp_sum(c1);
+        c2 = warp_sum(c2);
+        if (lane == 0) { out[5 * DKP] = c1; out[5 * DKP + 1] = c2; out[5 * DKP + 2] = 0.f; out[5 * DKP + 3] = 0.f; }
     }
-    c1 = block_sum(c1, red);
-    c2 = block_sum(c2, red);
-    if (threadIdx.x == 0) { out[5 * DKP] = c1; out[5 * DKP + 1] = c2; out[5 * DKP + 2] = 0.f; out[5 * DKP + 3] = 0.f; }
 }
 
 // Which row of its column lane l keeps in register ii: groups of four consecutive rows dealt round robin over the 8
@@ -234,8 +272,24 @@ int oe_gdelta_prepare(float* packed, const float* proj, long long ld, int off_r,
     if (n_tokens <= 0) return 0;
     const int DKP = padded_dk(dk);
     if (DKP < 0 || H < 1 || H > 65535 || rank < 0 || rank > 8192) return OE_ERR_UNSUPPORTED;
-    return oe_launch(gdelta_prepare_kernel, dim3(n_tokens, H), dim3(128), (size_t)(rank > 0 ? rank : 1) * sizeof(float), st,
-                     packed, proj, ld, off_r, off_k, off_a, off_z1, rank, w2, w0, a_bias, decay_coef, tok_seq, H, dk, DKP);
+    // the sums of a token are formed in the same order whatever the tile, so the tile's size changes no bit
+    const int tile = n_tokens >= 1024 ? 16 : (n_tokens >= 64 ? 8 : (n_tokens >= 4 ? PREP_WARPS : 1));
+    const size_t w2_bytes = (size_t)(dk | 1) * rank * sizeof(float);
+    const int w2_smem = tile >= 8 && w2_bytes <= 64 * 1024 && rank > 0;
+    const size_t smem = (size_t)tile * (rank > 0 ? rank : 1) * sizeof(float) + (w2_smem ? w2_bytes : 0);
+    const int ne = dk <= 32 ? 1 : (dk <= 64 ? 2 : (dk <= 128 ? 4 : 8));
+    auto go = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return oe_launch(kernel, dim3((n_tokens + tile - 1) / tile, H), dim3(PREP_WARPS * 32), smem, st, packed, proj, ld, off_r,
+                         off_k, off_a, off_z1, rank, w2, w0, a_bias, decay_coef, tok_seq, n_tokens, H, dk, DKP, tile, w2_smem);
+    };
+    if (ne == 1) return go(gdelta_prepare_kernel<1>);
+    if (ne == 2) return go(gdelta_prepare_kernel<2>);
+    if (ne == 4) return go(gdelta_prepare_kernel<4>);
+    return go(gdelta_prepare_kernel<8>);
 }
 
 // o [T, H dv] float32; state [slots, H, dk, dv] float32; packed as gdelta_prepare left it; v: the value columns of the
