@@ -195,7 +195,7 @@ def run_rope(a):
 
 
 def run_scan(a):
-    """The scans of the recurrent mixers (csrc/recurrent.cu) on `batch` sequences of `tokens` tokens each, against the
+    """The scans of the recurrent mixers (csrc/recurrent.cu, csrc/general_delta.cu) on `batch` sequences of `tokens` tokens each, against the
     recurrence written out in float64 for the first sequence's first head (up to 64 tokens)."""
     dev = torch.device("cuda:0")
     T, B, H, d = a.tokens, a.batch, a.heads, a.dim
@@ -221,6 +221,37 @@ def run_scan(a):
         us = timed(lambda i: ops.delta_rule_scan(o, state, qkv, gb, ctx, G, H, d, d), a.iters, a.once)
         nbytes = (qkv.numel() + gb.numel() + o.numel() + 2 * state.numel()) * 4
         report(f"delta_rule_scan tokens={T} batch={B} heads={H} ({d} x {d})", us, nbytes, 6.0 * T * B * H * d * d, err)
+        return
+    if a.kind == "general":
+        import math
+        C, rank, c = H * d, a.rank, math.exp(-0.5)
+        proj = torch.randn(T * B, 4 * C + rank, device=dev) * 0.3           # [r | k | a | v | z1]
+        w2, w0g = torch.randn(C, rank, device=dev) * 0.3, torch.randn(C, device=dev) - 3
+        ab = torch.randn(C, device=dev)
+        tok_seq = torch.zeros(T * B, dtype=torch.int32, device=dev)
+        packed = torch.empty(T * B, H, 5 * ops.gdelta_padded_dk(d) + 4, device=dev)
+        state = torch.zeros(B, H, d, d, device=dev)
+        o = torch.empty(T * B, C, device=dev)
+        vv = proj[:, 3 * C:4 * C]
+        prep = lambda i: ops.gdelta_prepare(packed, proj, 0, C, 2 * C, 4 * C, rank, w2, w0g, ab, c, tok_seq, H, d)   # noqa: E731
+        prep(0)
+        ops.gdelta_scan(o, state, packed, vv, ctx, H, d, d)
+        S = torch.zeros(d, d, dtype=torch.float64)
+        err = 0.0
+        pd = proj[:n].double().cpu()
+        dec = torch.exp(-c * torch.sigmoid(torch.tanh(pd[:, 4 * C:]) @ w2[:d].double().cpu().T + w0g[:d].double().cpu()))
+        for t in range(n):
+            rr, kk, vt = pd[t, :d], pd[t, C:C + d], pd[t, 3 * C:3 * C + d]
+            aa = torch.sigmoid(pd[t, 2 * C:2 * C + d] + ab[:d].double().cpu())
+            uu = kk / torch.sqrt((kk * kk).sum() + 1e-6)
+            S = dec[t][:, None] * S - torch.outer(aa * uu, uu @ S) + torch.outer(kk, vt)
+            err = max(err, (o[t, :d].double().cpu() - S.T @ rr).abs().max().item())
+        us = timed(prep, a.iters, a.once)
+        report(f"gdelta_prepare tokens={T} batch={B} heads={H} ({d}, rank {rank})", us,
+               (packed.numel() + proj.numel()) * 4, 2.0 * T * B * C * rank, 0.0)
+        us = timed(lambda i: ops.gdelta_scan(o, state, packed, vv, ctx, H, d, d), a.iters, a.once)
+        nbytes = (packed.numel() + 2 * o.numel() + 2 * state.numel()) * 4
+        report(f"gdelta_scan tokens={T} batch={B} heads={H} ({d} x {d})", us, nbytes, 8.0 * T * B * H * d * d, err)
         return
     r, k, v, z = (torch.randn(T * B, H * d, device=dev) * 0.1 for _ in range(4))
     u, w0 = torch.randn(H * d, device=dev), torch.randn(H * d, device=dev) - 3
@@ -282,7 +313,8 @@ def main(argv=None):
     r.add_argument("--kv-heads", type=int, default=8)
     r.add_argument("--head-dim", type=int, default=128)
     sc = sub.add_parser("scan")
-    sc.add_argument("--kind", default="delta", choices=["delta", "decay"])
+    sc.add_argument("--kind", default="delta", choices=["delta", "decay", "general"])
+    sc.add_argument("--rank", type=int, default=64, help="general: the rank of the decay's two-matrix projection")
     sc.add_argument("--tokens", type=int, default=2048)
     sc.add_argument("--batch", type=int, default=1)
     sc.add_argument("--heads", type=int, default=16)
