@@ -85,6 +85,34 @@ REAL = config(1000, 1024, 1e-6, [
     layer(delta(4, 128, 64), moe(8, 2, 256, 7.0))],
     scale=8.0, bigram=(4093, 31, 17), logit_scale=0.5, loop=(1, 3, 2))
 
+def random_config(rng):
+    """A configuration drawn from `rng` (random.Random): 2 to 6 layers of either kind in any order, sizes that are and
+    are not multiples of 16, every optional part present or absent, a loop anywhere or none."""
+    width = rng.choice([128, 192, 256, 320, 200])
+    n_layers = rng.randint(2, 6)
+    layers = []
+    for _ in range(n_layers):
+        mlp = None if rng.random() < 0.2 else moe(rng.choice([4, 8, 12, 16]), rng.choice([1, 2, 3]), rng.choice([32, 64, 96]),
+                                                  rng.choice([1.0, 1.5, 3.0]))
+        if rng.random() < 0.6:
+            heads = rng.choice([2, 4, 6, 8])
+            kv = rng.choice([k for k in (1, 2, 4, 8) if heads % k == 0])
+            dim, vdim = rng.choice([32, 48, 64, 96, 128, 40]), rng.choice([32, 48, 64, 96, 128, 24])
+            dims = rng.choice([d for d in (0, 8, 16, 24, 32, dim) if d <= dim])
+            sc = rng.choice([None, scaling(8.0, 1.0, 4.0, rng.choice([64, 2048])), scaling(4.0, 2.0, 8.0, 256)])
+            rotation = None if rng.random() < 0.1 else rot(dims, rng.choice([10000.0, 50000.0, 500.0]), sc)
+            layers.append(layer(attention(heads, kv, dim, vdim, dim ** -0.5, rng.choice([None, 17, 64, 96, 128, 200]), rotation), mlp))
+        else:
+            layers.append(layer(delta(rng.choice([1, 2, 4, 6]), rng.choice([16, 32, 48, 64, 96]), rng.choice([4, 16, 32])), mlp))
+    loop = None
+    if rng.random() < 0.7:
+        a = rng.randint(0, n_layers - 1)
+        loop = (a, rng.randint(a + 1, n_layers), rng.randint(1, 3))
+    bigram = None if rng.random() < 0.2 else (rng.choice([509, 1021, 4093]), rng.choice([31, 7, 1]), rng.choice([17, 3, 1]))
+    return config(rng.choice([256, 512, 1000]), width, rng.choice([1e-5, 1e-6]), layers, scale=rng.choice([0.25, 1.0, 4.0]),
+                  bigram=bigram, logit_scale=rng.choice([None, 0.25, 2.0]), loop=loop)
+
+
 ALL = {"B1": (B1, 3), "B2": (B2, 4), "B3": (B3, 5), "SHARP": (SHARP, 6), "LONG_MEMORY": (LONG_MEMORY, 8)}
 
 

@@ -470,6 +470,28 @@ def test_real_sizes(tmp_path, dtype):
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Layers of either kind in any order and number, sizes that are and are not multiples of 16, optional parts present
+    or absent, loops anywhere: whole prompts, a prompt and 34 single tokens, and a ragged batch, in both precisions.
+    float32 is held to three times the usual tolerance: among random models some are ill conditioned (the plain model
+    itself, run in float32, then differs from float64 by as much)."""
+    import random
+    raw = bm.random_config(random.Random(seed))
+    folder = bm.write(tmp_path / "m", raw, seed, std=0.06, router_scale=2.0)
+    plain = pb.PlainBogupel(folder)
+    lens = [1, 45, 230, 131]
+    requests = [helpers.random_tokens(n, raw["vocab"], 7 * seed + i) for i, n in enumerate(lens)]
+    for dtype in ("float32", "bfloat16"):
+        eng = _engine(folder, dtype, max_tokens=2048)
+        runs = {"whole": helpers.whole_steps(requests), "tail": helpers.tail_steps(requests, 34),
+                "batched": helpers.batched_steps(requests, [max(1, n - 20) for n in lens], 4)}
+        for k, steps in runs.items():
+            got = _run(eng, tmp_path / f"{dtype}{k}", steps, requests)
+            _compare(got, plain, requests, 3 * TOL[dtype] if dtype == "float32" else TOL[dtype], f"random {seed} {dtype} {k}")
+        eng.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_slots_and_pages_are_used_again(models, tmp_path, dtype):
     """Two slots for six requests: a request that starts in a slot another left reads nothing of it: neither keys and
