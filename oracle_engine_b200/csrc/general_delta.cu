@@ -189,6 +189,7 @@ gdelta_scan_kernel(float* o, float* state, const float* packed, const float* v, 
         else cp_async_wait<0>();
         __syncthreads();
         const float* base = stage_mem + buf * stagef;
+#pragma unroll 2
         for (int tt = 0; tt < cn; tt++) {
             const float* tk = base + tt * TOKF;
             const float4* w4 = reinterpret_cast<const float4*>(tk);
